@@ -93,6 +93,8 @@ class CacheGroup:
         self.pages = FreeList(num_pages, "page")
         if request.token_shape is not None:
             shape = (PAGE_TOKENS, *request.token_shape)            # the mixer's own record per token
+        elif request.value_heads is not None:
+            shape = (request.num_kv_heads + request.value_heads, PAGE_TOKENS, request.head_dim)
         else:
             shape = (2, request.num_kv_heads, PAGE_TOKENS, request.head_dim)
         self.pool = torch.zeros((len(entries), num_pages, *shape), dtype=request.dtype or dtype, device=device)
@@ -124,11 +126,15 @@ class CacheGroup:
             self.block_table[slot, a:a + need] = torch.tensor(new, dtype=torch.int32)
 
     def trim(self, slot: int, length: int) -> None:
-        """Window groups: give back the pages whose keys can no longer be read.  The
-        next query sits at position ``length`` and reads keys >= length + 1 - window."""
-        if not self.window:
+        """Window and chunk groups: give back the pages whose keys can no longer be read.  The
+        next query sits at position ``length`` and reads keys >= length + 1 - window, and with
+        chunks none before the start of its own chunk."""
+        chunk = self.request.chunk
+        if not self.window and not chunk:
             return
-        first_needed = max(0, length + 1 - self.window)
+        first_needed = max(0, length + 1 - self.window) if self.window else 0
+        if chunk:
+            first_needed = max(first_needed, length - length % chunk)
         have = self.slot_pages.get(slot, [])
         back = []
         for lp in range(min(len(have), first_needed // PAGE_TOKENS)):
@@ -153,7 +159,7 @@ class KVCache:
 
     def __init__(self, schedule: Sequence[ScheduleEntry], requests: Sequence[Optional[CacheRequest]],
                  states: Sequence[Optional[StateRequest]], max_tokens: int, max_slots: int,
-                 max_seq_len: int, dtype: torch.dtype, device):
+                 max_seq_len: int, dtype: torch.dtype, device, embedding_state: Optional[StateRequest] = None):
         self.device = device
         self.dtype = dtype
         self.num_pages = pages_for(max_tokens)
@@ -192,7 +198,8 @@ class KVCache:
                     raise ValueError(f"schedule[{i}] reads the cache of entry {src}, which keeps none")
                 g, j = where[src]
                 if e.cache_of is not None and (g.request.num_kv_heads, g.request.head_dim, g.request.token_shape,
-                                               g.request.dtype) != (r.num_kv_heads, r.head_dim, r.token_shape, r.dtype):
+                                               g.request.dtype, g.request.value_heads) != (
+                                                   r.num_kv_heads, r.head_dim, r.token_shape, r.dtype, r.value_heads):
                     raise ValueError(f"schedule[{i}] cannot read the cache of entry {src}: different head layout")
                 view = CacheView(pool=g.pool[j], block_table=g.block_table, writes=e.cache_of is None, group=g)
             st = None
@@ -200,6 +207,12 @@ class KVCache:
                 st = torch.zeros((self.max_slots, *s.shape), dtype=s.dtype, device=device)
                 self.state_tensors.append(st)
             self.ios.append(LayerIO(cache=view, state=st))
+        # state that the embedding keeps per sequence (``embedding_state``: what it asked for, or None)
+        self.embedding_io = LayerIO()
+        if embedding_state is not None:
+            st = torch.zeros((self.max_slots, *embedding_state.shape), dtype=embedding_state.dtype, device=device)
+            self.state_tensors.append(st)
+            self.embedding_io = LayerIO(state=st)
 
     # ---- slots ------------------------------------------------------------------
     def alloc_slot(self) -> int:

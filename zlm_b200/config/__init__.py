@@ -2,6 +2,7 @@ from .spec import (ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry)
 from .qwen3 import Qwen3Config
 from .nuvilorn import NuvilornConfig
 from .zekazen import ZekazenConfig
+from .lodevik import LodevikConfig
 
 __all__ = ["ConfigError", "LayerSpec", "ModelSpec", "PartSpec", "ScheduleEntry", "Qwen3Config", "NuvilornConfig",
-           "ZekazenConfig"]
+           "ZekazenConfig", "LodevikConfig"]

@@ -9,6 +9,11 @@
 // (src/kernels/transformer/attention.zig:86-164); kv head = q head / group
 // (:104-105); window start: seq = pos + 1, t_start = seq - w if w and seq > w
 // (src/runtime/executor.zig:93-98).
+// Options: `chunk` (keys of the query's own chunk of that many positions, counted from position 0, only),
+// `softcap` (s <- cap * tanh(s / cap) after the scale), `sinks` (one number per query head whose exponential
+// joins the softmax's denominator without a value; without the array the flag `sink` stands for a 0), and
+// `v_share` (that many neighbouring key heads read one value head: the page is [nkv key heads | nkv / v_share
+// value heads] of [ZLM_PAGE][hd] each).
 #include "common.cuh"
 
 #define ATT_WARPS 4
@@ -20,7 +25,8 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
                          int q_stride, const TA* __restrict__ pool,
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ token_pos, const int* __restrict__ token_slot,
-                         int nq, int nkv, int hd, float scale, int window, int sink) {
+                         int nq, int nkv, int hd, float scale, int window, int sink, int chunk, float softcap,
+                         const float* __restrict__ sinks, int v_share) {
     extern __shared__ float sm[];
     float* qs = sm;                         // [hd]
     float* accs = sm + hd;                  // [ATT_WARPS][hd]
@@ -33,10 +39,11 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
     const int pos = token_pos[t];
     const int slot = token_slot[t];
     const int seq = pos + 1;
-    const int t_start = (window != 0 && seq > window) ? seq - window : 0;
+    int t_start = (window != 0 && seq > window) ? seq - window : 0;
+    if (chunk > 0) t_start = max(t_start, pos - pos % chunk);
     const int* pages = block_table + (size_t)slot * table_stride;
-    const size_t page_stride = (size_t)2 * nkv * ZLM_PAGE * hd;
-    const size_t v_off = (size_t)nkv * ZLM_PAGE * hd;
+    const size_t page_stride = (size_t)(nkv + nkv / v_share) * ZLM_PAGE * hd;
+    const size_t v_off = (size_t)(nkv - kvh + kvh / v_share) * ZLM_PAGE * hd;       // from this key head to its value head
 
     const TA* qp = q + (size_t)t * q_stride + (size_t)h * hd;
     if (!ZLM_CHK(qp, (size_t)hd * sizeof(TA)) ||
@@ -46,7 +53,10 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
     __syncthreads();
 
     float m = -INFINITY, l = 0.f;
-    if (sink && warp == 0) { m = 0.f; l = 1.f; }      // a key of score 0 without a value: one more term in the sum
+    if (sink && warp == 0) {      // one more term in the sum, without a value: exp(sinks[h]), or exp(0)
+        m = (sinks && ZLM_CHK(sinks + h, 4)) ? sinks[h] : 0.f;
+        l = 1.f;
+    }
     float acc[ATT_MAX_PER_LANE];
 #pragma unroll
     for (int r = 0; r < ATT_MAX_PER_LANE; ++r) acc[r] = 0.f;
@@ -68,6 +78,7 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
             float d = 0.f;
             for (int e = 0; e < hd; ++e) d = fmaf(qs[e], to_f32(kr[e]), d);
             s = d * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
         }
         const float cm = warp_max(s);          // the chunk holds at least one valid key
         const float mn = fmaxf(m, cm);
@@ -122,8 +133,11 @@ extern "C" int zlm_attention_generic(void* out, int out_stride, const void* q, i
                                      int dtype, const void* pool, const int* block_table,
                                      int table_stride, const int* token_pos,
                                      const int* token_slot, int T, int nq, int nkv, int hd,
-                                     float scale, int window, int sink, cudaStream_t st) {
+                                     float scale, int window, int sink, int chunk, float softcap,
+                                     const float* sinks, int v_share, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(chunk >= 0 && softcap >= 0.f && v_share >= 1 && nkv % v_share == 0,
+                "attention: chunk=%d softcap=%f, %d key heads a value head over %d key heads", chunk, softcap, v_share, nkv);
     ZLM_REQUIRE(hd > 0 && hd <= 32 * ATT_MAX_PER_LANE, "attention: head_dim=%d must be at most %d", hd,
                 32 * ATT_MAX_PER_LANE);
     ZLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention: %d query heads over %d kv heads", nq, nkv);
@@ -135,12 +149,12 @@ extern "C" int zlm_attention_generic(void* out, int out_stride, const void* q, i
     if (dtype == ZLM_DTYPE_F32)
         attention_generic_kernel<float><<<grid, ATT_WARPS * 32, smem, st>>>(
             (float*)out, out_stride, (const float*)q, q_stride, (const float*)pool, block_table,
-            table_stride, token_pos, token_slot, nq, nkv, hd, scale, window, sink);
+            table_stride, token_pos, token_slot, nq, nkv, hd, scale, window, sink, chunk, softcap, sinks, v_share);
     else if (dtype == ZLM_DTYPE_BF16)
         attention_generic_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, smem, st>>>(
             (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)pool, block_table, table_stride, token_pos, token_slot, nq, nkv,
-            hd, scale, window, sink);
+            hd, scale, window, sink, chunk, softcap, sinks, v_share);
     else
         ZLM_REQUIRE(false, "attention: unsupported dtype %d", dtype);
     return zlm_check_launch("attention_generic");

@@ -210,14 +210,16 @@ extern "C" int zlm_head_linear(void* out, int out_stride, int out_hstride, const
 // ---------------------------------------------------------------------------- attention, any size
 // One block per (token, head).  The keys are walked in chunks of 32 aligned to absolute positions
 // and dealt round-robin to the 4 warps (a lane takes one key of the chunk), then the warps are merged
-// in a fixed order.  q is [T, H, r + dr] (folded query | rotated part), out [T, H, r].
+// in a fixed order.  q is [T, H, r + dr] (folded query | rotated part), out [T, H, r].  `sinks` (optional): one
+// number per head whose exponential joins the softmax's denominator without a value; `chunk`: only the keys of the
+// query's own chunk of that many positions, counted from position 0.
 #define LAT_WARPS 4
 template <typename TA, int NPL>
 __global__ void __launch_bounds__(LAT_WARPS * 32)
 latent_attention_kernel(TA* __restrict__ out, int out_stride, const TA* __restrict__ q, int q_stride,
                         const TA* __restrict__ pool, const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ token_pos, const int* __restrict__ token_slot, int H, int r, int dr,
-                        float scale, int window) {
+                        float scale, int window, int chunk, const float* __restrict__ sinks) {
     extern __shared__ float sm[];
     const int D = r + dr;
     float* qs = sm;                         // [D]
@@ -229,7 +231,8 @@ latent_attention_kernel(TA* __restrict__ out, int out_stride, const TA* __restri
     if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4)) return;
     const int pos = token_pos[t], slot = token_slot[t];
     const int seq = pos + 1;
-    const int t_start = (window != 0 && seq > window) ? seq - window : 0;
+    int t_start = (window != 0 && seq > window) ? seq - window : 0;
+    if (chunk > 0) t_start = max(t_start, pos - pos % chunk);
     const int* pages = block_table + (size_t)slot * table_stride;
     pdl_wait();
     const TA* qp = q + (size_t)t * q_stride + (size_t)h * D;
@@ -239,6 +242,7 @@ latent_attention_kernel(TA* __restrict__ out, int out_stride, const TA* __restri
     __syncthreads();
 
     float m = -INFINITY, l = 0.f;
+    if (sinks && warp == 0 && ZLM_CHK(sinks + h, 4)) { m = sinks[h]; l = 1.f; }      // exp(sinks[h]): a term without a value
     float acc[NPL];
 #pragma unroll
     for (int i = 0; i < NPL; ++i) acc[i] = 0.f;
@@ -304,7 +308,8 @@ latent_attention_kernel(TA* __restrict__ out, int out_stride, const TA* __restri
 template <typename TA>
 static int launch_latent_attention(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                    const int* block_table, int table_stride, const int* token_pos, const int* token_slot,
-                                   int T, int H, int r, int dr, float scale, int window, cudaStream_t st) {
+                                   int T, int H, int r, int dr, float scale, int window, int chunk, const float* sinks,
+                                   cudaStream_t st) {
     dim3 grid(T, H);
     const size_t smem = (size_t)(r + dr + LAT_WARPS * r) * sizeof(float);
 #define ZLM_LAT(NPL)                                                                                                  \
@@ -315,7 +320,7 @@ static int launch_latent_attention(void* out, int out_stride, const void* q, int
             big[zlm_device_index()] = true;                                                                           \
         }                                                                                                             \
         zlm_launch(latent_attention_kernel<TA, NPL>, grid, LAT_WARPS * 32, smem, st, (TA*)out, out_stride, (const TA*)q, \
-                   q_stride, (const TA*)pool, block_table, table_stride, token_pos, token_slot, H, r, dr, scale, window); \
+                   q_stride, (const TA*)pool, block_table, table_stride, token_pos, token_slot, H, r, dr, scale, window, chunk, sinks); \
     } while (0)
     if (r <= 128) ZLM_LAT(4);
     else if (r <= 512) ZLM_LAT(16);
@@ -327,17 +332,17 @@ static int launch_latent_attention(void* out, int out_stride, const void* q, int
 extern "C" int zlm_latent_attention(void* out, int out_stride, const void* q, int q_stride, int dtype, const void* pool,
                                     const int* block_table, int table_stride, const int* token_pos,
                                     const int* token_slot, int T, int H, int r, int dr, float scale, int window,
-                                    cudaStream_t st) {
+                                    int chunk, const float* sinks, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
     ZLM_REQUIRE(H > 0 && H <= 65535 && r > 0 && r <= 1024 && dr >= 0 && dr <= 1024,
                 "latent_attention: heads=%d kv_rank=%d rot_dim=%d (kv_rank and rot_dim at most 1024)", H, r, dr);
-    ZLM_REQUIRE(window >= 0, "latent_attention: window=%d", window);
+    ZLM_REQUIRE(window >= 0 && chunk >= 0, "latent_attention: window=%d chunk=%d", window, chunk);
     if (dtype == ZLM_DTYPE_F32)
         return launch_latent_attention<float>(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,
-                                              token_slot, T, H, r, dr, scale, window, st);
+                                              token_slot, T, H, r, dr, scale, window, chunk, sinks, st);
     if (dtype == ZLM_DTYPE_BF16)
         return launch_latent_attention<__nv_bfloat16>(out, out_stride, q, q_stride, pool, block_table, table_stride,
-                                                      token_pos, token_slot, T, H, r, dr, scale, window, st);
+                                                      token_pos, token_slot, T, H, r, dr, scale, window, chunk, sinks, st);
     ZLM_REQUIRE(false, "latent_attention: unsupported dtype %d", dtype);
     return ZLM_OK;
 }

@@ -57,7 +57,8 @@ class Engine:
         self.max_seq_len = int(min(max_seq_len or self.spec.max_position, self.spec.max_position, self.max_tokens))
         self.max_batch = int(max_batch or min(pages, 256))
         self.cache = KVCache(self.spec.schedule, self.model.cache_requests(), self.model.state_requests(),
-                             self.max_tokens, self.max_batch, self.max_seq_len, dtype, self.device)
+                             self.max_tokens, self.max_batch, self.max_seq_len, dtype, self.device,
+                             embedding_state=self.model.embedding_state_request())
         self.max_step_tokens = int(max_step_tokens or self.max_tokens)
         self.layout = MetaLayout(self.max_step_tokens, self.max_batch)
         self.stager = MetaStager(self.layout, self.device)
@@ -160,7 +161,7 @@ class Engine:
         forget = getattr(self.rt.k, "forget_pending", None)
         if forget is not None:
             forget()            # (only a step that raised half-way leaves anything)
-        hidden = self.model.forward(ctx, self.cache.ios)
+        hidden = self.model.forward(ctx, self.cache.ios, self.cache.embedding_io)
         logits = self.model.logits(hidden, self.stager.view("want_rows", wanted), wanted) if wanted else None
         flush = getattr(self.rt.k, "flush_shares", None)
         if flush is not None:

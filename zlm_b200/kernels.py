@@ -168,6 +168,7 @@ class CudaKernels:
         self._norm_halves = None       # (stream, rows times weight, sums of squares, blocks, weight): a product left them
         self._lazy_ok = False          # the next norm's output is read by products only (the arrangement's word)
         self._lazy = None              # (out, stream, weight, eps, rows times weight, sums of squares, blocks): a norm not run
+        self._blank = None             # a tensor that is to be taken as zeros (see expect_blank)
         self._scratch = {}
         self.scratch_generation = 0
         self._launches = 0
@@ -217,6 +218,9 @@ class CudaKernels:
                 self._ranges = noted
         if self._lazy is not None or self._norm_halves is not None:
             self._touch_norms(t)
+        if self._blank is not None and self._overlap(t, self._blank):
+            blank, self._blank = self._blank, None
+            blank.zero_()           # somebody other than the expected product comes first: the zeros are made real
         if self.bounds_check:
             self._ranges.append((t.data_ptr(), _span_bytes(t)))
         return c_void_p(t.data_ptr())
@@ -260,7 +264,7 @@ class CudaKernels:
         """Drops what one call left for a later one (shares of K, a norm's halves, a norm not run, the
         arrangement's words) without finishing any of it: for the start of a step, where anything still
         pending belongs to a step that was given up."""
-        self._shares = self._norm_hint = self._norm_halves = self._lazy = None
+        self._shares = self._norm_hint = self._norm_halves = self._lazy = self._blank = None
         self._lazy_ok = False
 
     def finish_norm(self) -> None:
@@ -395,6 +399,11 @@ class CudaKernels:
         ldx, ldy = x.stride(0), out.stride(0)
         if accumulate:
             assert out.dtype == torch.float32
+            blank = self._blank
+            if (blank is not None and blank.data_ptr() == out.data_ptr() and tuple(blank.shape) == tuple(out.shape)
+                    and out.is_contiguous()):
+                self._blank = None
+                accumulate = defer = False       # adding to zeros: a plain store of the fp32 sums
         if x.dtype == torch.float32:
             assert out.dtype == torch.float32 and ldx == K
             self._call("zlm_gemm_f32", self._p(out), self._p(x),
@@ -615,19 +624,32 @@ class CudaKernels:
     def attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                   token_pos: torch.Tensor, token_slot: torch.Tensor, nq: int, nkv: int, hd: int,
                   scale: float, window: int, plan=None, len_bucket: Optional[int] = None,
-                  v_dim: Optional[int] = None, sink: bool = False) -> None:
+                  v_dim: Optional[int] = None, sink: bool = False, chunk: int = 0, softcap: float = 0.0,
+                  sinks: Optional[torch.Tensor] = None, v_share: int = 1) -> None:
         """out[t, h] = softmax(q[t, h] . K * scale) V over the keys [start, pos[t]] of the
         token's slot; q may be a column view of the fused qkv buffer.  ``plan`` is the
         step's context (one token per sequence: the split-KV kernel; whole prompts or
         chunks: the flash kernels; none: the generic kernel); ``len_bucket`` is the longest
         sequence in pages as ``attention_len_bucket`` rounds it (computed if absent).  ``sink``: the
         softmax's denominator is 1 + sum exp(s), as if one more key of score 0 without a value stood
-        in every row."""
+        in every row; ``sinks`` [nq] fp32: that key's score is sinks[h] instead of 0.  ``chunk``: a query sees
+        only the keys of its own chunk of that many positions (counted from position 0 of the sequence).
+        ``softcap``: scores become softcap * tanh(score / softcap) after the scale.  ``v_share``: that many
+        neighbouring key heads read one value head; a page of the pool is then [nkv key heads | nkv / v_share
+        value heads] of [PAGE_TOKENS, hd] each (with 1, the ordinary [2, nkv, PAGE_TOKENS, hd])."""
         T = q.shape[0]
+        if sinks is not None:
+            assert sinks.dtype == torch.float32 and sinks.shape == (nq,) and sinks.is_contiguous()
+            sink = True
         sk = c_int(1 if sink else 0)
         assert out.shape == (T, nq * hd) and q.shape[1] == nq * hd and q.dtype == out.dtype == pool.dtype
         assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
-        assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
+        assert v_share >= 1 and nkv % v_share == 0 and chunk >= 0 and softcap >= 0
+        assert pool[0].numel() == (nkv + nkv // v_share) * PAGE_TOKENS * hd and pool.shape[-1] == hd
+        extra = (c_int(chunk), c_float(softcap), self._p(sinks), c_int(v_share))
+        plain = chunk == 0 and softcap == 0 and sinks is None and v_share == 1
+        if not plain:
+            plan = None         # (the options above: the kernel for any shape)
         if (plan is not None and plan.is_decode and q.dtype == torch.bfloat16
                 and self.lib.zlm_attention_decode_supported(nq, nkv, hd)):
             if len_bucket is None:
@@ -679,7 +701,7 @@ class CudaKernels:
                    self._p(q), c_int(q.stride(0)), c_int(_dt(q)), self._p(pool),
                    self._p(block_table), c_int(block_table.stride(0)),
                    self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
-                   c_int(nkv), c_int(hd), c_float(scale), c_int(window), sk, self._stream())
+                   c_int(nkv), c_int(hd), c_float(scale), c_int(window), sk, *extra, self._stream())
 
     # -- short convolution, retention, gated heads (see csrc/short_conv.cu, csrc/retention.cu) --------------
     def conv_norm_write(self, q_out: torch.Tensor, proj: torch.Tensor, conv_w: torch.Tensor, state: Optional[torch.Tensor],
@@ -838,14 +860,21 @@ class CudaKernels:
     def latent_attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                          token_pos: torch.Tensor, token_slot: torch.Tensor, heads: int, kv_rank: int, rot_dim: int,
                          scale: float, window: int = 0, plan=None, len_bucket: Optional[int] = None,
-                         impl: Optional[str] = None) -> None:
+                         impl: Optional[str] = None, chunk: int = 0, sinks: Optional[torch.Tensor] = None) -> None:
         """out[t, h, :kv_rank] = sum_j softmax_j(q[t, h] . rec_j * scale) rec_j[:kv_rank] over the records
         [start, pos[t]] of the token's slot in ``pool`` [pages, PAGE_TOKENS, kv_rank + rot_dim]: one
         key/value record per token that every head reads (q [T, heads * (kv_rank + rot_dim)]).  ``plan`` is
         the step's context: with it bf16 steps run on the tensor-core kernel where it takes the sizes (kv_rank
-        and rot_dim multiples of 16); without it, in 32-bit, or with ``impl="plain"``, the plain kernel runs."""
+        and rot_dim multiples of 16); without it, in 32-bit, or with ``impl="plain"``, the plain kernel runs.
+        ``sinks`` [heads] fp32: exp(sinks[h]) joins the softmax's denominator of head h, without a value.  ``chunk``:
+        a query sees only the records of its own chunk of that many positions."""
         T = q.shape[0]
         D = kv_rank + rot_dim
+        if sinks is not None:
+            assert sinks.dtype == torch.float32 and sinks.shape == (heads,) and sinks.is_contiguous()
+        if chunk or sinks is not None:
+            impl = "plain"
+
         assert q.shape[1] == heads * D and out.shape == (T, heads * kv_rank) and q.dtype == out.dtype == pool.dtype
         assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
         assert tuple(pool.shape[1:]) == (PAGE_TOKENS, D)
@@ -879,7 +908,108 @@ class CudaKernels:
         self._call("zlm_latent_attention", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
                    c_int(_dt(q)), self._p(pool), self._p(block_table), c_int(block_table.stride(0)),
                    self._p(token_pos), self._p(token_slot), c_int(T), c_int(heads), c_int(kv_rank), c_int(rot_dim),
-                   c_float(scale), c_int(window), self._stream())
+                   c_float(scale), c_int(window), c_int(chunk), self._p(sinks), self._stream())
+
+    # -- the stream of designs that norm a sublayer's output (see csrc/stream_ops.cu) -------------------------
+    def embed_scaled(self, out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, scale: float,
+                     pair: Optional[torch.Tensor] = None, buckets: int = 0, mul_prev: int = 0, mul_cur: int = 0,
+                     plan=None, prev_state: Optional[torch.Tensor] = None) -> None:
+        """out[t] = table[ids[t]] * scale, plus, with a ``pair`` table [buckets + 1, H], the row
+        (ids[t-1] * mul_prev + ids[t] * mul_cur) mod buckets (the row ``buckets`` for a sequence's first token).  The
+        token before a step's first one comes from ``prev_state`` [slots] int32, which then receives the step's last
+        token of every sequence."""
+        T, H = out.shape
+        assert out.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == H
+        assert out.is_contiguous() and table.is_contiguous()
+        if pair is not None:
+            assert pair.shape == (buckets + 1, H) and pair.dtype == table.dtype and pair.is_contiguous()
+            assert prev_state is not None and prev_state.dtype == torch.int32 and plan is not None
+        ll = ctypes.c_longlong
+        self._call("zlm_embed_scaled", self._p(out), self._p(table), c_int(_dt(table)), c_float(scale), self._p(pair),
+                   c_int(buckets), ll(mul_prev), ll(mul_cur), self._p(ids),
+                   self._p(plan.token_pos if pair is not None else None), self._p(plan.token_seq if pair is not None else None),
+                   self._p(plan.cu_seqlens if pair is not None else None), self._p(plan.seq_slot if pair is not None else None),
+                   self._p(prev_state if pair is not None else None), c_int(T), c_int(H), c_int(table.shape[0]), self._stream())
+
+    def norm_scale_add(self, stream: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float,
+                       layer_scale: Optional[torch.Tensor] = None) -> None:
+        """stream[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w (* layer_scale), in fp32; y fp32 or the compute dtype."""
+        R, H = stream.shape
+        assert stream.dtype == torch.float32 and y.shape == (R, H) and w.shape == (H,)
+        assert stream.is_contiguous() and y.is_contiguous() and w.is_contiguous()
+        assert layer_scale is None or (layer_scale.shape == (H,) and layer_scale.is_contiguous())
+        self._call("zlm_norm_scale_add", self._p(stream), self._p(y), c_int(_dt(y)), self._p(w), c_int(_dt(w)),
+                   self._p(layer_scale), c_int(_dt(layer_scale) if layer_scale is not None else F32), c_int(R), c_int(H),
+                   c_float(eps), self._stream())
+
+    def cast_rows(self, out: torch.Tensor, x: torch.Tensor) -> None:
+        """out = x rounded to bfloat16 (x fp32, both contiguous and of one shape)."""
+        assert x.dtype == torch.float32 and out.dtype == torch.bfloat16 and out.shape == x.shape
+        assert x.is_contiguous() and out.is_contiguous()
+        self._call("zlm_cast_rows", self._p(out), self._p(x), ctypes.c_longlong(x.numel()), self._stream())
+
+    def gated_act(self, out: torch.Tensor, gu: torch.Tensor, act: str = "silu") -> None:
+        """out[t, i] = act(gu[t, i]) * gu[t, I + i]; act "silu" or "gelu_tanh"."""
+        T, I = out.shape
+        assert gu.shape == (T, 2 * I) and gu.dtype == out.dtype and out.is_contiguous() and gu.is_contiguous()
+        self._call("zlm_gated_act", self._p(out), self._p(gu), c_int(_dt(out)), c_int(T), c_int(I),
+                   c_int({"silu": 0, "gelu_tanh": 1}[act]), self._stream())
+
+    def scale_(self, x: torch.Tensor, s: float) -> None:
+        """x *= s for a contiguous fp32 tensor (logits times a constant)."""
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        if self._candidates is not None and self._candidates[0] == x.data_ptr():
+            self._candidates = None         # the candidates a few-token product left hold the unscaled values
+        self._call("zlm_scale_f32", self._p(x), ctypes.c_longlong(x.numel()), c_float(s), self._stream())
+
+    def head_scalar_gate(self, x: torch.Tensor, g: torch.Tensor) -> None:
+        """x[t, h, :] *= sigmoid(g[t, h]) in place; x [T, heads, V] and g [T, heads] may be views (innermost contiguous)."""
+        T, H, V = x.shape
+        assert g.shape == (T, H) and g.dtype == x.dtype and x.stride(2) == 1 and g.stride(1) == 1
+        self._call("zlm_head_scalar_gate", self._p(x), c_int(x.stride(0)), c_int(x.stride(1)), self._p(g), c_int(g.stride(0)),
+                   c_int(_dt(x)), c_int(T), c_int(H), c_int(V), self._stream())
+
+    def expect_blank(self, t: Optional[torch.Tensor]) -> None:
+        """An arrangement's word that ``t`` (fp32) is to be taken as zeros although it holds anything: the next product
+        added into it, ``linear(t, ..., accumulate=True)``, stores instead of adding.  Whatever else is given ``t``
+        first through this class has it cleared then, so the word is never wrong."""
+        self._blank = t
+
+    # -- differential attention (see csrc/diff_attention.cu) --------------------------------------------------
+    def diff_prep(self, q_out: torch.Tensor, proj: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, eps: float,
+                  inv_freq: Optional[torch.Tensor], n_rot: int, token_pos: torch.Tensor, token_slot: torch.Tensor,
+                  block_table: torch.Tensor, pool: torch.Tensor, heads: int, kv_heads: int, dim: int, vdim: int) -> None:
+        """On the fused projection ``proj`` [T, >= (2 heads + 2 kv_heads) dim + kv_heads vdim] (columns [q: heads x 2 maps x
+        dim | k: kv_heads x 2 x dim | v: kv_heads x vdim]): every map of q and k is RMS-normed over dim (weights ``q_w``,
+        ``k_w``), its neighbouring pairs (2i, 2i+1), i < n_rot/2, are turned by pos * inv_freq[i]; q goes to ``q_out``
+        [T, 2 heads, hdp] as query heads (g*2 + m)*rep + j, k and v to the token's place of the paged ``pool``
+        [pages, 2 kv_heads key heads + kv_heads value heads, PAGE_TOKENS, hdp], padded with zeros to hdp."""
+        T = proj.shape[0]
+        hdp = pool.shape[-1]
+        assert proj.shape[1] >= (2 * heads + 2 * kv_heads) * dim + kv_heads * vdim and proj.stride(1) == 1
+        assert q_out.shape == (T, 2 * heads * hdp) and q_out.stride(1) == 1 and q_out.dtype == proj.dtype == pool.dtype
+        assert pool.is_contiguous() and pool[0].numel() == 3 * kv_heads * PAGE_TOKENS * hdp and block_table.dtype == torch.int32
+        assert q_w.shape == (dim,) and k_w.shape == (dim,) and q_w.dtype == k_w.dtype and q_w.is_contiguous() and k_w.is_contiguous()
+        if inv_freq is not None and n_rot:
+            assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot
+        else:
+            n_rot = 0
+        self._call("zlm_diff_prep", self._p(q_out), c_int(q_out.stride(0)), self._p(proj), c_int(proj.stride(0)),
+                   c_int(_dt(proj)), self._p(q_w), self._p(k_w), c_int(_dt(q_w)), c_float(eps),
+                   self._p(inv_freq if n_rot else None), c_int(n_rot), self._p(token_pos), self._p(token_slot),
+                   self._p(block_table), c_int(block_table.stride(0)), self._p(pool), c_int(T), c_int(heads), c_int(kv_heads),
+                   c_int(dim), c_int(vdim), c_int(hdp), self._stream())
+
+    def diff_combine(self, out: torch.Tensor, a: torch.Tensor, heads: int, kv_heads: int, vdim: int, hdp: int, lam: float,
+                     post: float, eps: float) -> None:
+        """out[t, h, :] = unit_rms(a1 - lam * a2) * post over vdim, where a1, a2 are the attention's outputs of head h's
+        two maps in ``a`` [T, 2 heads, hdp] (the order ``diff_prep`` gives the query heads)."""
+        T = a.shape[0]
+        assert a.shape == (T, 2 * heads * hdp) and out.shape == (T, heads * vdim) and a.dtype == out.dtype
+        assert a.stride(1) == 1 and out.stride(1) == 1
+        self._call("zlm_diff_combine", self._p(out), c_int(out.stride(0)), self._p(a), c_int(a.stride(0)), c_int(_dt(a)),
+                   c_int(T), c_int(heads), c_int(kv_heads), c_int(vdim), c_int(hdp), c_float(lam), c_float(post), c_float(eps),
+                   self._stream())
 
     # -- routed experts (see csrc/moe.cu) -------------------------------------
     def moe_route(self, idx: torch.Tensor, wgt: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, top: int,

@@ -53,12 +53,19 @@ class CacheRequest:
     ``token_shape`` and, if it is not the compute dtype, its ``dtype``: the pool is then
     [pages, PAGE_TOKENS, *token_shape], paged, sized, trimmed by the window and given back
     like any other, and read by the mixer's own code (``num_kv_heads`` and ``head_dim``
-    are then only part of what tells one group of layers from another)."""
+    are then only part of what tells one group of layers from another).
+
+    ``chunk``: queries read only the keys of their own chunk of that many positions (counted from position 0), so the
+    pages of the chunks before may be given back like those that left a window.  ``value_heads``: keys and values have
+    different numbers of heads (several key heads read one value head); a page is then
+    [num_kv_heads key heads | value_heads value heads] of [PAGE_TOKENS, head_dim] each."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     token_shape: Optional[Tuple[int, ...]] = None
     dtype: Optional[torch.dtype] = None
+    chunk: int = 0
+    value_heads: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -221,6 +228,14 @@ class Norm(Part):
 
     def forward(self, out: torch.Tensor, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
+
+    def add_into(self, stream: torch.Tensor, y: torch.Tensor) -> None:
+        """stream += norm(y), in fp32, for arrangements that norm a sublayer's output (y fp32 [T, H]).  A norm with a
+        kernel for it overrides this; the default norms into scratch and adds."""
+        out = self.rt.ws.get("norm.add_into", y.shape, torch.float32)
+        self.forward(out, y)
+        self.finish_products()
+        stream.add_(out)
 
 
 class PositionEncoding(Part):

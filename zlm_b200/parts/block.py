@@ -3,6 +3,10 @@
 ``pre_norm``: h = h + mixer(norm(h)); h = h + ffn(norm(h)), plain adds in fp32
 (src/architectures/impl/qwen3/block.zig:21-41).  The parts add their output
 into the stream themselves, so the last projection of each can carry the add.
+
+``sublayer_norm``: h = h + norm(mixer(h)); h = h + norm(ffn(h)): the norm stands on the sublayer's *output*, the
+sublayers read the stream itself.  The norm may carry a scale per coordinate of its own (``rms_norm`` with
+``layer_scale``); norm, scale and the residual add are one kernel in fp32.
 """
 from __future__ import annotations
 
@@ -75,3 +79,53 @@ class PreNormBlock(Part):
         self.ffn.forward(x, hidden, ctx)
         if expect is not None:
             expect(None)
+
+
+@register_arrangement("sublayer_norm")
+class SublayerNormBlock(Part):
+    """x <- x + norm1(mixer(x)), then x <- x + norm2(ffn(x)).  The parts still "add their result into the stream they
+    are given": they are given a scratch row per token that counts as zeros (the kernel object's ``expect_blank``:
+    the part's last product stores instead of adding), and the norm adds its result into the real stream
+    (``Norm.add_into``).  In bfloat16 the sublayer's input is the stream rounded once per sublayer."""
+
+    def __init__(self, hidden_size: int, mixer: Mixer, feed_forward: FeedForward,
+                 mixer_norm: Norm, feed_forward_norm: Norm):
+        self.hidden = int(hidden_size)
+        self.mixer, self.ffn = mixer, feed_forward
+        self.mixer_norm, self.ffn_norm = mixer_norm, feed_forward_norm
+
+    children = PreNormBlock.children
+    graph_safe = PreNormBlock.graph_safe
+    prefers_plain_launches = PreNormBlock.prefers_plain_launches
+    step_key = PreNormBlock.step_key
+
+    def first_norm_weight(self):
+        return None             # the block's first reader of the stream is not a norm
+
+    def _sublayer(self, part, norm: Norm, hidden: torch.Tensor, run) -> None:
+        rt, k = self.rt, self.rt.k
+        self.finish_products()          # (a block of another arrangement before this one may have left its last product)
+        if rt.dtype == torch.float32:
+            x = hidden
+        else:
+            x = rt.ws.get("block.input", hidden.shape, rt.dtype)
+            k.cast_rows(x, hidden)
+        y = rt.ws.get("block.sublayer_out", hidden.shape, torch.float32)
+        blank = getattr(k, "expect_blank", None)
+        if blank is not None:
+            blank(y)
+        else:
+            y.zero_()
+        run(x, y)
+        if blank is not None:
+            blank(None)
+        norm.add_into(hidden, y)
+
+    def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
+        for word in ("expect_norm", "norm_output_read_by_products"):
+            say = getattr(self.rt.k, word, None)
+            if say is not None:
+                say(None if word == "expect_norm" else False)
+        self._sublayer(self.mixer, self.mixer_norm, hidden, lambda x, y: self.mixer.forward(x, y, ctx, io))
+        if not getattr(self.ffn, "is_identity", False):
+            self._sublayer(self.ffn, self.ffn_norm, hidden, lambda x, y: self.ffn.forward(x, y, ctx))

@@ -10,6 +10,11 @@ With h the mixer's input, per token:
     k_h = [W_uk_h c | kr],  v_h = W_uv_h c
     score_h(i, j) = (q_h(i) . k_h(j)) * scale,  j in the window ending at i;  softmax;  y = W_o [heads' outputs]
 
+Options: ``sink`` (a learned number per head, tensor ``sink`` [heads], whose exponential joins the softmax's denominator:
+it has no key and no value and is not scaled), ``gate`` (head h's output is multiplied by sigmoid(W_g h)_h, tensor ``g``
+[heads, hidden], one number per head from the mixer's own input) and ``chunk`` (a query sees only the keys of its own
+chunk of that many positions, counted from position 0).
+
 The cache record of a token is [c | kr] (``CacheRequest.token_shape``); a layer built with
 ``kv_proj=False`` has no W_dkv and reads the records of the schedule entry its own entry names
 (``ScheduleEntry.cache_of``), with its own W_uk, W_uv, queries and everything else.
@@ -40,13 +45,16 @@ class LatentAttention(Mixer):
 
     def __init__(self, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_dim: int, kv_rank: int,
                  scale: float, norm_eps: float = 1e-6, window: int = 0,
-                 position: Optional[Mapping[str, Any]] = None, kv_proj: bool = True):
+                 position: Optional[Mapping[str, Any]] = None, kv_proj: bool = True, sink: bool = False,
+                 gate: bool = False, chunk: int = 0):
         self.hidden = int(hidden_size)
         self.H, self.dn, self.dr, self.dv, self.r = int(num_heads), int(head_dim), int(rot_dim), int(v_dim), int(kv_rank)
         if min(self.H, self.dv, self.r) <= 0 or self.dn < 0 or self.dr < 0 or self.dn + self.dr <= 0:
             raise ValueError("latent attention: heads, v_dim, kv_rank and dim + rot_dim must be positive")
         self.scale, self.eps, self.window = float(scale), float(norm_eps), int(window)
         self.kv_proj = bool(kv_proj)
+        self.sink, self.gate, self.chunk = bool(sink), bool(gate), int(chunk)
+        self.sinks: Optional[torch.Tensor] = None
         position = dict(position or {"kind": "none"})
         self.position = lookup(POSITION_ENCODINGS, "position encoding", position.pop("kind"))(**position)
         if not getattr(self.position, "fused", False) or not (getattr(self.position, "interleaved", False)
@@ -67,10 +75,14 @@ class LatentAttention(Mixer):
         if self.kv_proj:
             s["dkv"] = ParamSpec((self.R, self.hidden))
             s["dkv.norm"] = ParamSpec((self.r,), kind="vector", init="one_plus_normal")
+        if self.sink:
+            s["sink"] = ParamSpec((self.H,), kind="vector", init="normal")
+        if self.gate:
+            s["g"] = ParamSpec((self.H, self.hidden))
         return s
 
     def cache_request(self) -> Optional[CacheRequest]:
-        return CacheRequest(1, self.R, self.window, token_shape=(self.R,))
+        return CacheRequest(1, self.R, self.window, token_shape=(self.R,), chunk=self.chunk)
 
     def attach(self, rt) -> None:
         super().attach(rt)
@@ -87,12 +99,23 @@ class LatentAttention(Mixer):
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         H, dn, dv, r = self.H, self.dn, self.dv, self.r
         w_q = params.pop("q")
+        # one fused projection: rows [q | c_raw | kr_raw | gate], with rows of zeros up to a multiple of 8
+        rows = [w_q]
         if self.kv_proj:
-            # one fused projection: rows [q | c_raw | kr_raw]
-            self.w_in = torch.cat([w_q, params.pop("dkv")], dim=0).contiguous()
+            rows.append(params.pop("dkv"))
             self.c_norm = params.pop("dkv.norm")
         else:
-            self.w_in, self.c_norm = w_q, None
+            self.c_norm = None
+        self.g_off = sum(w.shape[0] for w in rows)
+        if self.gate:
+            rows.append(params.pop("g"))
+            n = self.g_off + H
+            if n % 8:
+                rows.append(torch.zeros((8 - n % 8, self.hidden), dtype=w_q.dtype, device=w_q.device))
+        self.w_in = torch.cat(rows, dim=0).contiguous() if len(rows) > 1 else w_q
+        self.N_in = self.w_in.shape[0]
+        if self.sink:
+            self.sinks = params.pop("sink").float().contiguous()
         # per head: W_uk_h^T [r, dn] (folds into the query), W_uv_h [dv, r] (unfolds the output)
         self.w_uk_t = params.pop("uk").view(H, dn, r).transpose(1, 2).contiguous()
         self.w_uv = params.pop("uv").view(H, dv, r).contiguous()
@@ -104,7 +127,7 @@ class LatentAttention(Mixer):
         hd = dn + self.dr
         self.unfoldable = bool(
             self.w_o.dtype == torch.bfloat16 and hd % 16 == 0 and 16 <= hd <= 192 and dv <= hd and r % 8 == 0
-            and self.R % 8 == 0 and (self.Q + (self.R if self.kv_proj else 0)) % 8 == 0
+            and self.R % 8 == 0 and self.Q % 8 == 0 and self.N_in % 8 == 0
             and hasattr(self.rt.k, "latent_unfold"))
         if self.unfoldable:
             self.w_ukv = torch.cat([self.w_uk_t.transpose(1, 2).reshape(H * dn, r), self.w_uv.reshape(H * dv, r)]).contiguous()
@@ -117,8 +140,12 @@ class LatentAttention(Mixer):
                "uk": self.w_uk_t.transpose(1, 2).reshape(self.H * self.dn, self.r),
                "uv": self.w_uv.reshape(self.H * self.dv, self.r)}
         if self.kv_proj:
-            out["dkv"] = self.w_in[self.Q:]
+            out["dkv"] = self.w_in[self.Q: self.Q + self.R]
             out["dkv.norm"] = self.c_norm
+        if self.sink:
+            out["sink"] = self.sinks
+        if self.gate:
+            out["g"] = self.w_in[self.g_off: self.g_off + self.H]
         return out
 
     # ---- the step -----------------------------------------------------------
@@ -137,13 +164,13 @@ class LatentAttention(Mixer):
                 and not any(ctx.h_seq_start)):
             self._forward_unfolded(x, residual, ctx, cache, writes)
             return
-        qd = rt.ws.get("lat.qd", (T, self.Q + (R if writes else 0)), rt.dtype)
+        qd = rt.ws.get("lat.qd", (T, self.N_in), rt.dtype)
         k.linear(qd, x, self.w_in)
         q = qd[:, : self.Q]
-        q3 = q.view(T, H, self.Dq) if not writes else qd.as_strided((T, H, self.Dq), (qd.stride(0), self.Dq, 1))
+        q3 = qd.as_strided((T, H, self.Dq), (qd.stride(0), self.Dq, 1))
         # the folded query [q' | rotated part] of every head
         ql = rt.ws.get("lat.ql", (T, H, R), rt.dtype)
-        k.latent_prep(q, ql[:, :, r:], qd[:, self.Q:] if writes else None, self.c_norm, self.eps,
+        k.latent_prep(q, ql[:, :, r:], qd[:, self.Q: self.Q + R] if writes else None, self.c_norm, self.eps,
                       self.position.inv_freq, self.position.n_rot, ctx.token_pos, ctx.token_slot,
                       cache.block_table, cache.pool, H, dn, dr, r)
         if dn:
@@ -153,10 +180,22 @@ class LatentAttention(Mixer):
         ol = rt.ws.get("lat.ol", (T, H * r), rt.dtype)
         key = self.step_key(ctx)
         k.latent_attention(ol, ql.view(T, H * R), cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot,
-                           H, r, dr, self.scale, self.window, ctx, len_bucket=key[1] if key else None)
+                           H, r, dr, self.scale, self.window, ctx, len_bucket=key[1] if key else None,
+                           **self._options())
         ov = rt.ws.get("lat.ov", (T, H * dv), rt.dtype)
         k.head_linear(ov.view(T, H, dv), ol.view(T, H, r), self.w_uv)
+        if self.gate:
+            k.head_scalar_gate(ov.view(T, H, dv), qd[:, self.g_off: self.g_off + H])
         k.linear(residual, ov, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next
+
+    def _options(self) -> Dict[str, Any]:
+        """The attention kernels' words for the sink and the chunks (none of them for a mixer without)."""
+        o: Dict[str, Any] = {}
+        if self.sink:
+            o["sinks"] = self.sinks
+        if self.chunk:
+            o["chunk"] = self.chunk
+        return o
 
     def _step_pages(self, ctx: StepContext):
         """Pages for the step's own tokens, sequence after sequence (whole prompts: positions start at 0), as a table
@@ -186,12 +225,12 @@ class LatentAttention(Mixer):
         T = x.shape[0]
         H, dn, dr, dv, r, R = self.H, self.dn, self.dr, self.dv, self.r, self.R
         hd = dn + dr
-        qd = rt.ws.get("lat.qd", (T, self.Q + (R if writes else 0)), rt.dtype)
+        qd = rt.ws.get("lat.qd", (T, self.N_in), rt.dtype)
         k.linear(qd, x, self.w_in)
         q = qd[:, : self.Q]
-        q3 = q.view(T, H, self.Dq)
+        q3 = qd.as_strided((T, H, self.Dq), (qd.stride(0), self.Dq, 1))
         # rotated query parts in place; the records into their pages
-        k.latent_prep(q, q3[:, :, dn:], qd[:, self.Q:] if writes else None, self.c_norm, self.eps,
+        k.latent_prep(q, q3[:, :, dn:], qd[:, self.Q: self.Q + R] if writes else None, self.c_norm, self.eps,
                       self.position.inv_freq, self.position.n_rot, ctx.token_pos, ctx.token_slot,
                       cache.block_table, cache.pool, H, dn, dr, r)
         rec = rt.ws.get("lat.rec", (T, R), rt.dtype)
@@ -212,5 +251,7 @@ class LatentAttention(Mixer):
                                      h_seq_start=ctx.h_seq_start, h_seq_new=ctx.h_seq_new)
         ao = rt.ws.get("lat.ao", (T, H * hd), rt.dtype)
         k.attention(ao, q, spool, table, ctx.token_pos, ctx.token_seq, H, H, hd, self.scale, self.window, plan,
-                    v_dim=dv)
+                    v_dim=dv, **self._options())
+        if self.gate:
+            k.head_scalar_gate(ao.view(T, H, hd), qd[:, self.g_off: self.g_off + H])
         k.linear(residual, ao, self.w_o_pad, accumulate=True, defer=True)      # a norm reads the stream next

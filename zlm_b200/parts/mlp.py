@@ -18,9 +18,14 @@ from .base import FeedForward, ParamSpec, StepContext
 class SwiGLU(FeedForward):
     reads_input_by_products = True       # x goes into the gate/up product and nowhere else
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+        """``activation``: what the gate passes through, "silu" or "gelu_tanh"
+        (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
         self.hidden = int(hidden_size)
         self.inter = int(intermediate_size)
+        if activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: activation={activation!r}")
+        self.act = activation
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
@@ -31,7 +36,7 @@ class SwiGLU(FeedForward):
         gate, up = params.pop("gate_proj.weight"), params.pop("up_proj.weight")
         # bf16: gate and up rows interleaved in eights, so that the product's epilogue holds
         # a channel's gate and up together and writes silu(gate) * up directly
-        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 8 == 0
+        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 8 == 0 and self.act == "silu"
                       and hasattr(self.rt.k, "linear_swiglu"))
         if self.fused:
             from ..kernels import interleave_gate_up
@@ -59,5 +64,8 @@ class SwiGLU(FeedForward):
         else:
             gu = rt.ws.get("ffn.gu", (T, 2 * self.inter), rt.dtype)
             k.linear(gu, x, self.w_gu)
-            k.swiglu(act, gu)
+            if self.act == "silu":
+                k.swiglu(act, gu)
+            else:
+                k.gated_act(act, gu, self.act)
         k.linear(residual, act, self.w_down, accumulate=True, defer=True)      # a norm reads the stream next

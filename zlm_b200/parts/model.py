@@ -96,6 +96,12 @@ class DecoderModel:
     def state_requests(self) -> List[Optional[StateRequest]]:
         return [self.blocks[e.layer].mixer.state_request() for e in self.spec.schedule]
 
+    def embedding_state_request(self) -> Optional[StateRequest]:
+        """Per-sequence state that the embedding keeps (the token before a step's first one, for a table looked up by
+        pairs of tokens), or None."""
+        ask = getattr(self.embedding, "state_request", None)
+        return ask() if ask is not None else None
+
     @property
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks)
@@ -119,12 +125,15 @@ class DecoderModel:
         return tuple(seen)
 
     # ---- the step -------------------------------------------------------------
-    def forward(self, ctx: StepContext, ios: List[LayerIO]) -> torch.Tensor:
+    def forward(self, ctx: StepContext, ios: List[LayerIO], embedding_io: Optional[LayerIO] = None) -> torch.Tensor:
         """Runs the step's tokens through every schedule entry; returns the fp32
-        residual stream [T, hidden]."""
+        residual stream [T, hidden].  ``embedding_io``: the embedding's per-sequence state, if it asked for any."""
         rt = self.rt
         hidden = rt.ws.get("model.hidden", (ctx.T, self.spec.hidden_size), torch.float32)
-        self.embedding.forward(hidden, ctx.token_ids)
+        if getattr(self.embedding, "uses_step", False):
+            self.embedding.forward(hidden, ctx.token_ids, ctx, embedding_io)
+        else:
+            self.embedding.forward(hidden, ctx.token_ids)
         sched = self.spec.schedule
         for i, (e, io) in enumerate(zip(sched, ios)):
             # who reads the stream after this block: the next block's first norm (the final norm reads

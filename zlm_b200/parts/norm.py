@@ -2,7 +2,8 @@
 
 y = (x * 1/sqrt(mean(x^2) + eps)) * w, weight used as it is
 (src/kernels/transformer/norm.zig:4-37).  ``scalar``: the checkpoint holds one gain for the whole
-row (a tensor without dimensions) instead of a weight per coordinate.
+row (a tensor without dimensions) instead of a weight per coordinate.  ``layer_scale``: a second vector ``scale``
+multiplies the normed row coordinate by coordinate (a layer's learned scale on its sublayer's output).
 """
 from __future__ import annotations
 
@@ -18,18 +19,25 @@ from .base import Norm, ParamSpec
 class RMSNorm(Norm):
     reads_stream_by_kernel = True
 
-    def __init__(self, size: int, eps: float, scalar: bool = False):
+    def __init__(self, size: int, eps: float, scalar: bool = False, layer_scale: bool = False):
         self.size = int(size)
         self.eps = float(eps)
         self.scalar = bool(scalar)
+        self.layer_scale = bool(layer_scale)
         self.weight: Optional[torch.Tensor] = None
         self.gain: Optional[torch.Tensor] = None
+        self.scale: Optional[torch.Tensor] = None
+        self.reads_stream_by_kernel = not self.layer_scale      # (with a scale the plain norm kernel is not the whole norm)
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec(() if self.scalar else (self.size,), kind="vector", init="one_plus_normal")}
+        s = {"weight": ParamSpec(() if self.scalar else (self.size,), kind="vector", init="one_plus_normal")}
+        if self.layer_scale:
+            s["scale"] = ParamSpec((self.size,), kind="vector", init="one_plus_normal")
+        return s
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         self.weight = params["weight"]
+        self.scale = params.get("scale")
         if self.scalar:
             # the kernels (and the products that fold a norm in) read a weight per coordinate: the one
             # gain, widened to 32 bits (exact), repeated along the row
@@ -37,10 +45,26 @@ class RMSNorm(Norm):
             self.weight = self.gain.float().reshape(1).expand(self.size).contiguous()
 
     def tensors(self) -> Dict[str, torch.Tensor]:
-        return {"weight": self.gain if self.scalar else self.weight}
+        out = {"weight": self.gain if self.scalar else self.weight}
+        if self.layer_scale:
+            out["scale"] = self.scale
+        return out
 
     def forward(self, out: torch.Tensor, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
-        self.rt.k.rmsnorm(out, x, self.weight, self.eps, rows)
+        w = self.weight
+        if self.layer_scale:
+            # norm weight and scale as one vector (their fp32 product, made once)
+            if getattr(self, "_w_scaled", None) is None:
+                self._w_scaled = (self.weight.float() * self.scale.float()).contiguous()
+            w = self._w_scaled
+        self.rt.k.rmsnorm(out, x, w, self.eps, rows)
+
+    def add_into(self, stream: torch.Tensor, y: torch.Tensor) -> None:
+        fused = getattr(self.rt.k, "norm_scale_add", None)
+        if fused is None:
+            super().add_into(stream, y)
+            return
+        fused(stream, y, self.weight, self.eps, self.scale if self.layer_scale else None)
 
 
 @register_norm("none")
