@@ -82,6 +82,16 @@ def softmax_with_sink(s: torch.Tensor, ok: torch.Tensor, sink: Optional[torch.Te
     return e / den
 
 
+def attend(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, ok: torch.Tensor, softcap: float = 0.0,
+           sink: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q, k [n, heads, d], v [n, heads, dv], ok [n, n] -> [n, heads, dv]: p = softmax_j(cap(q_i . k_j * scale)) over
+    the visible j, cap(s) = softcap * tanh(s / softcap) (softcap 0: none), the sink in the denominator only."""
+    s = torch.einsum("ihd,jhd->hij", q.to(F), k.to(F)) * scale
+    if softcap:
+        s = softcap * torch.tanh(s / softcap)
+    return torch.einsum("hij,jhd->ihd", softmax_with_sink(s, ok, sink), v.to(F))
+
+
 def latent_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], heads: int, dim: int, rot_dim: int, vdim: int,
                      kv_rank: int, scale: float, rot_base: float, rot_dims: int, eps: float,
                      chunk: int = 0) -> torch.Tensor:
@@ -95,9 +105,10 @@ def latent_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], heads: int,
     qr = rotate_pairs(q[:, :, dim:], pos, rot_base, rot_dims)
     k = (c @ w["uk"].to(F).T).view(n, heads, dim)
     v = (c @ w["uv"].to(F).T).view(n, heads, vdim)
-    s = (torch.einsum("ihd,jhd->hij", q[:, :, :dim], k) + torch.einsum("ihd,jd->hij", qr, kr)) * scale
-    p = softmax_with_sink(s, visible(n, chunk), w.get("sink"))
-    o = torch.einsum("hij,jhd->ihd", p, v)
+    # a head's key is [its own unrotated part | the rotated part that all heads share]
+    qq = torch.cat([q[:, :, :dim], qr], dim=-1)
+    kk = torch.cat([k, kr[:, None, :].expand(n, heads, rot_dim)], dim=-1)
+    o = attend(qq, kk, v, scale, visible(n, chunk), 0.0, w.get("sink"))
     if "g" in w:
         o = o * torch.sigmoid(h @ w["g"].to(F).T)[:, :, None]
     return o.reshape(n, heads * vdim) @ w["o"].to(F).T
@@ -126,12 +137,7 @@ def diff_attention(h: torch.Tensor, w: Mapping[str, torch.Tensor], heads: int, k
     vv = v.repeat_interleave(rep, dim=1)
     ok = visible(n, chunk)
     lam = diff_lambda(w, diff)
-    maps = []
-    for m in range(2):
-        s = torch.einsum("ihd,jhd->hij", q[:, :, m], kk[:, :, m]) * scale
-        if softcap:
-            s = softcap * torch.tanh(s / softcap)
-        maps.append(torch.einsum("hij,jhd->ihd", softmax_with_sink(s, ok), vv))
+    maps = [attend(q[:, :, m], kk[:, :, m], vv, scale, ok, softcap) for m in range(2)]
     o = unit_rms(maps[0] - lam * maps[1], eps) * (1.0 - diff)
     return o.reshape(n, heads * vdim) @ w["o"].to(F).T
 
