@@ -551,7 +551,32 @@ ZEKAZEN_SIZES = {
     # width 4096, 32 heads over 8, 4 layers, 2 experts of 2048 a token
     "wide": (_zekazen(4096, 32, 8, 4096, 30, 2, 2, 2048, 4, 3, "araa", 32768), _twin(4096, 32, 8, 4096, 4, 32768)),
 }
-DESIGNS = {"nuvilorn": ("Nuvilorn", DESIGN_SIZES), "zekazen": ("Zekazen", ZEKAZEN_SIZES)}
+def _lodevik(width, heads, kv_heads, chunk, ff, kinds, vocab):
+    """Latent-attention layers (heads of 128 + 64 over latents of 512, a sink and a gate per head; at width 1024 half of
+    that) and differential-attention layers (two maps of 64 a head over values of 128: a head does the multiply-adds of
+    a twin's head of 128) in turn, gated gelu feed-forwards of the twin's size, a table of token pairs."""
+    half = width <= 1024
+    lat = {"heads": heads, "dim": 64 if half else 128, "rot_dim": 32 if half else 64, "vdim": 64 if half else 128,
+           "kv_rank": 256 if half else 512, "scale": (96 if half else 192) ** -0.5,
+           "rot": {"base": 250000.0, "dims": 32 if half else 64}}
+    att = {"heads": heads, "kv_heads": kv_heads, "dim": 32 if half else 64, "vdim": 64 if half else 128,
+           "scale": (32 if half else 64) ** -0.5, "softcap": 50.0, "diff": 0.3, "mask": {"size": chunk},
+           "rot": {"base": 50000.0, "dims": 16 if half else 32}}
+    return {"architecture": "Lodevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "layers": [{"type": "attention" if k == "a" else "latent_attention", "mixer": dict(att if k == "a" else lat),
+                        "mlp": {"kind": "dense", "ff": ff}} for k in kinds]}
+
+
+# Lodevik: latent and differential layers in turn, chunks that cover the run (so that the differential attention does
+# the work of the twin's) or a quarter of it ("small"), the twin's feed-forward size
+LODEVIK_SIZES = {
+    "lite": (_lodevik(2048, 16, 4, 4096, 6144, "lalala", 32768), _twin(2048, 16, 4, 6144, 6, 32768)),
+    "small": (_lodevik(1024, 8, 2, 512, 3072, "lalala", 32768), _twin(1024, 8, 2, 3072, 6, 32768)),
+    "wide": (_lodevik(4096, 32, 8, 4096, 12288, "lala", 32768), _twin(4096, 32, 8, 12288, 4, 32768)),
+}
+DESIGNS = {"nuvilorn": ("Nuvilorn", DESIGN_SIZES), "zekazen": ("Zekazen", ZEKAZEN_SIZES),
+           "lodevik": ("Lodevik", LODEVIK_SIZES)}
 
 
 def design_comparison(args) -> int:

@@ -5,7 +5,7 @@ edge, the first tokens of a sequence, and greedy generation through ``Engine.gen
 import pytest
 import torch
 
-from lodevik_helpers import LODE, assert_rows_close, greedy_generate, make_model, oracle_logits, prompts
+from lodevik_helpers import LODE, MEDIAN_TOL, assert_rows_close, greedy_generate, make_model, oracle_logits, prompts
 
 pytestmark = pytest.mark.gpu
 
@@ -149,7 +149,9 @@ def test_chunk_pages_come_back_while_a_sequence_grows(tmp_path):
 def test_greedy_generation(tmp_path, name, dtype):
     """``Engine.generate`` (scheduler, decode graphs with the slots' last tokens inside them, sampler) against the
     oracle's greedy continuation.  32-bit: the same tokens.  bfloat16: every chosen token is, for the oracle given the
-    engine's own tokens so far, the best one or within rounding of it."""
+    engine's own tokens so far, the best one or within rounding of it: a bfloat16 row differs from the oracle's by
+    MEDIAN_TOL of its norm, which is that share of the row's root mean square a logit; two logits differ by sqrt(2)
+    times that, and four such deviations are allowed."""
     eng, cfg, ref = build(tmp_path, name, dtype)
     ps = prompts(cfg["vocab"], [5, 40, 1, 66], seed=60)
     n = 12
@@ -161,11 +163,37 @@ def test_greedy_generation(tmp_path, name, dtype):
         else:
             lg = oracle_logits(ref, cfg, list(p) + list(o))[len(p) - 1:-1]
             gap = lg.max(dim=-1).values - lg[torch.arange(n), torch.tensor(o)]
-            assert bool((gap <= 0.05 * lg.std(dim=-1)).all()), f"{name}: a chosen token is {gap.max():.3f} below the best"
+            allowed = 4 * 2 ** 0.5 * MEDIAN_TOL["bfloat16"] * lg.pow(2).mean(dim=-1).sqrt()
+            assert bool((gap <= allowed).all()), f"{name}: a chosen token is {gap.max():.3f} below the best"
     eng.check(sync=True)
     # a second run in the same engine: captured decode steps are replayed on slots that were used before
     again = eng.generate(ps, max_tokens=n).tokens
     assert again == out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_replayed_decode_steps_give_the_logits_of_the_plain_implementation(tmp_path, name, dtype):
+    """The sampler's decode steps (captured once, then replayed) against the oracle row by row: a captured step must
+    contain every kernel of the eager one, also those that a note left in the step's context could make it skip."""
+    from zlm_b200.sampling import SamplingParams
+    eng, cfg, ref = build(tmp_path, name, dtype)
+    ps = prompts(cfg["vocab"], [9, 70, 33], seed=77)
+    more = prompts(cfg["vocab"], [10, 10, 10], seed=78)
+    greedy = SamplingParams(temperature=0.0)
+    for _ in range(2):          # the second round replays from its first step on
+        slots = [eng.new_sequence() for _ in ps]
+        eng.prefill_sample(slots, ps, greedy, [0, 1, 2])
+        rows = []
+        for t in range(10):
+            eng.decode_sample(slots, [m[t] for m in more], greedy, [0, 1, 2])
+            rows.append(eng.last_logits[: len(ps)].clone())
+        for i, (p, m) in enumerate(zip(ps, more)):
+            want = oracle_logits(ref, cfg, list(p) + list(m))[len(p):]
+            assert_rows_close(torch.stack([r[i] for r in rows]), want, dtype, f"{name} replayed decode, request {i}")
+        for s in slots:
+            eng.release(s)
+    assert eng.decoder.replays > 0 or not eng.decoder.use_graphs
 
 
 def test_weights_read_back_by_name(tmp_path):

@@ -25,30 +25,31 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ token_pos, const int* __restrict__ token_slot, int nq, int nkv,
                         float scale_log2, int window, int splits, int per, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int fresh, int sink) {
+                        float* __restrict__ part_ml, int fresh, int sink, AttnOpts opt) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     attention_decode_item<HD, true>(smem_raw, threadIdx.x, GroupSync{0, DEC_THREADS}, blockIdx.x, blockIdx.y,
                                     blockIdx.z, out, out_stride, q, q_stride, pool, block_table, table_stride,
-                                    token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml, fresh, sink);
+                                    token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml, fresh, sink, opt);
 }
 
 __global__ void __launch_bounds__(COMB_THREADS)
 attention_decode_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const float* __restrict__ part_o,
                                 const float* __restrict__ part_ml, const int* __restrict__ token_pos, int nq,
-                                int hd, int splits, int per, int window) {
+                                int hd, int splits, int per, int window, int chunk) {
     __shared__ float fs[COMB_MAX_SPLITS];
     __shared__ float red[32];
     pdl_trigger();
     pdl_wait();
     attention_decode_combine_item(fs, red, threadIdx.x, GroupSync{0, COMB_THREADS}, blockIdx.x, blockIdx.y, out,
-                                  out_stride, part_o, part_ml, token_pos, nq, hd, splits, per, window);
+                                  out_stride, part_o, part_ml, token_pos, nq, hd, splits, per, window, chunk);
 }
 
 template <int HD>
 static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride,
                          const __nv_bfloat16* pool, const int* block_table, int table_stride,
                          const int* token_pos, const int* token_slot, int T, int nq, int nkv, float scale,
-                         int window, int splits, int per, float* part_o, float* part_ml, int fresh, int sink, cudaStream_t st) {
+                         int window, int splits, int per, float* part_o, float* part_ml, int fresh, int sink, AttnOpts opt,
+                         cudaStream_t st) {
     const size_t stage_bytes = (size_t)4 * ZLM_PAGE * HD * sizeof(__nv_bfloat16);
     const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
@@ -65,12 +66,12 @@ static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16
     dim3 grid(T, nkv, splits);
     const float scale_log2 = scale * 1.4426950408889634f;
     zlm_launch(kern, grid, dim3(DEC_THREADS), smem, st, out, out_stride, q, q_stride, pool, block_table, table_stride,
-               token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml, fresh, sink);
+               token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml, fresh, sink, opt);
     int rc = zlm_check_launch("attention_decode");
     if (rc) return rc;
     if (splits > 1) {
         zlm_launch(attention_decode_combine_kernel, dim3(T, nq), dim3(COMB_THREADS), 0, st, out, out_stride,
-                   (const float*)part_o, (const float*)part_ml, token_pos, nq, HD, splits, per, window);
+                   (const float*)part_o, (const float*)part_ml, token_pos, nq, HD, splits, per, window, opt.chunk);
         rc = zlm_check_launch("attention_decode_combine");
     }
     return rc;
@@ -78,15 +79,22 @@ static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16
 
 // The combine step alone, for other split attention kernels that leave (max, sum, O) per split in the same
 // layout: part_o [T][nq][splits][hd], part_ml [T][nq][splits][2] (maxima in base-2 exponents).
+// chunk: the splits start at the page of the first key that a query reads, which the chunk moves as the window does.
+extern "C" int zlm_attention_decode_combine_chunk(void* out, int out_stride, const float* part_o, const float* part_ml,
+                                                  const int* token_pos, int T, int nq, int hd, int splits, int per,
+                                                  int window, int chunk, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(splits >= 1 && splits <= COMB_MAX_SPLITS && nq > 0 && nq <= 65535 && hd > 0 && per >= 1 && chunk >= 0,
+                "attention_decode_combine: splits=%d heads=%d size=%d", splits, nq, hd);
+    zlm_launch(attention_decode_combine_kernel, dim3(T, nq), dim3(COMB_THREADS), 0, st, (__nv_bfloat16*)out, out_stride,
+               part_o, part_ml, token_pos, nq, hd, splits, per, window, chunk);
+    return zlm_check_launch("attention_decode_combine");
+}
+
 extern "C" int zlm_attention_decode_combine(void* out, int out_stride, const float* part_o, const float* part_ml,
                                             const int* token_pos, int T, int nq, int hd, int splits, int per, int window,
                                             cudaStream_t st) {
-    if (T == 0) return ZLM_OK;
-    ZLM_REQUIRE(splits >= 1 && splits <= COMB_MAX_SPLITS && nq > 0 && nq <= 65535 && hd > 0 && per >= 1,
-                "attention_decode_combine: splits=%d heads=%d size=%d", splits, nq, hd);
-    zlm_launch(attention_decode_combine_kernel, dim3(T, nq), dim3(COMB_THREADS), 0, st, (__nv_bfloat16*)out, out_stride,
-               part_o, part_ml, token_pos, nq, hd, splits, per, window);
-    return zlm_check_launch("attention_decode_combine");
+    return zlm_attention_decode_combine_chunk(out, out_stride, part_o, part_ml, token_pos, T, nq, hd, splits, per, window, 0, st);
 }
 
 // 1 if this kernel takes the shape, 0 if the caller has to use the generic kernel
@@ -100,12 +108,17 @@ extern "C" int zlm_attention_decode_supported(int nq, int nkv, int hd) {
 // (1 for a decode step); pages that hold older positions only are read before the wait for the
 // kernel before this one.  0: not known, nothing is read early.
 // sink: the softmax has one more term, a key of score 0 that has no value (its denominator is 1 + sum exp(s)).
+// chunk, softcap, sinks, v_share: the options of AttnOpts (attn_common.cuh).
 extern "C" int zlm_attention_decode_fresh(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                           const int* block_table, int table_stride, const int* token_pos,
                                           const int* token_slot, int T, int nq, int nkv, int hd, float scale,
                                           int window, int splits, int per, float* part_o, float* part_ml,
-                                          int fresh, int sink, cudaStream_t st) {
+                                          int fresh, int sink, int chunk, float softcap, const float* sinks,
+                                          int v_share, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(chunk >= 0 && softcap >= 0.f && v_share >= 1 && nkv % v_share == 0,
+                "attention_decode: chunk=%d softcap=%g v_share=%d", chunk, (double)softcap, v_share);
+    const AttnOpts opt{chunk, softcap, sinks, v_share};
     ZLM_REQUIRE(zlm_attention_decode_supported(nq, nkv, hd),
                 "attention_decode: %d heads over %d kv heads of size %d is not a shape this kernel takes", nq, nkv, hd);
     ZLM_REQUIRE(splits >= 1 && splits <= COMB_MAX_SPLITS && nkv <= 65535 && per >= 1,
@@ -117,7 +130,7 @@ extern "C" int zlm_attention_decode_fresh(void* out, int out_stride, const void*
     case H:                                                                                                   \
         return launch_decode<H>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,           \
                                 (const __nv_bfloat16*)pool, block_table, table_stride, token_pos, token_slot, \
-                                T, nq, nkv, scale, window, splits, per, part_o, part_ml, fresh, sink, st);
+                                T, nq, nkv, scale, window, splits, per, part_o, part_ml, fresh, sink, opt, st);
     switch (hd) {
         ZLM_DEC_CASE(16) ZLM_DEC_CASE(32) ZLM_DEC_CASE(48) ZLM_DEC_CASE(64) ZLM_DEC_CASE(80) ZLM_DEC_CASE(96)
         ZLM_DEC_CASE(112) ZLM_DEC_CASE(128)
@@ -132,7 +145,8 @@ extern "C" int zlm_attention_decode(void* out, int out_stride, const void* q, in
                                     int window, int splits, int per, float* part_o, float* part_ml,
                                     cudaStream_t st) {
     return zlm_attention_decode_fresh(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,
-                                      token_slot, T, nq, nkv, hd, scale, window, splits, per, part_o, part_ml, 0, 0, st);
+                                      token_slot, T, nq, nkv, hd, scale, window, splits, per, part_o, part_ml, 0, 0,
+                                      0, 0.f, nullptr, 1, st);
 }
 
 // ---------------------------------------------------------------------------

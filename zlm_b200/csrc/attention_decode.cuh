@@ -16,7 +16,8 @@ __device__ __forceinline__ void attention_decode_item(
     unsigned char* smem_raw, const int tid, const GroupSync gs, const int t, const int kvh, const int split,
     __nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride, const __nv_bfloat16* pool,
     const int* block_table, int table_stride, const int* token_pos, const int* token_slot, int nq, int nkv,
-    float scale_log2, int window, int splits, int per, float* part_o, float* part_ml, int fresh, int sink = 0) {
+    float scale_log2, int window, int splits, int per, float* part_o, float* part_ml, int fresh, int sink = 0,
+    AttnOpts opt = AttnOpts{0, 0.f, nullptr, 1}) {
     constexpr int KS = HD / 16;            // k-steps of Q K^T; pairs of output n-tiles of P V
     constexpr int CH = HD / 8;             // 16-byte chunks per row
     constexpr int TILE = ZLM_PAGE * HD;    // elements of one K or V page of one kv head
@@ -30,11 +31,11 @@ __device__ __forceinline__ void attention_decode_item(
     if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4)) return;      // block-uniform
     const int pos = token_pos[t];
     const int slot = token_slot[t];
-    const int seq = pos + 1;
-    const int t_start = (window != 0 && seq > window) ? seq - window : 0;
+    const int t_start = attn_first_key(pos, window, opt.chunk);
     const int* pages = block_table + (size_t)slot * table_stride;
-    const size_t page_stride = (size_t)2 * nkv * TILE;
-    const size_t v_off = (size_t)nkv * TILE;
+    const size_t page_stride = (size_t)(nkv + nkv / opt.v_share) * TILE;
+    const size_t v_off = (size_t)(nkv - kvh + kvh / opt.v_share) * TILE;      // from this key head to its value head
+    const float softcap = opt.softcap;
 
     // this split's pages
     const int page_lo = t_start / ZLM_PAGE, page_hi = pos / ZLM_PAGE + 1;
@@ -101,8 +102,9 @@ __device__ __forceinline__ void attention_decode_item(
 #pragma unroll
         for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8
-    if (sink && split == 0 && warp == 0) {      // a key of score 0 without a value, counted once per (token, head)
-        m0 = m1 = 0.f;
+    if (sink && split == 0 && warp == 0) {      // a key of score 0 (or sinks[head]) without a value, counted once per (token, head)
+        m0 = g < G ? attn_sink_log2(opt.sinks, kvh * G + g) : 0.f;
+        m1 = g + 8 < G ? attn_sink_log2(opt.sinks, kvh * G + g + 8) : 0.f;
         if (qd == 0) l0 = l1 = 1.f;
     }
 
@@ -139,8 +141,8 @@ __device__ __forceinline__ void attention_decode_item(
             for (int e = 0; e < 2; ++e) {
                 const int key = kbase + nt * 8 + qd * 2 + e;
                 const bool ok = key <= pos && key >= t_start;
-                s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
-                s[nt][2 + e] = ok ? s[nt][2 + e] * scale_log2 : -INFINITY;
+                s[nt][e] = ok ? attn_score_log2(s[nt][e], scale_log2, softcap) : -INFINITY;
+                s[nt][2 + e] = ok ? attn_score_log2(s[nt][2 + e], scale_log2, softcap) : -INFINITY;
                 mx0 = fmaxf(mx0, s[nt][e]);
                 mx1 = fmaxf(mx1, s[nt][2 + e]);
             }
@@ -247,10 +249,10 @@ __device__ __forceinline__ void attention_decode_item(
 __device__ __forceinline__ void attention_decode_combine_item(
     float* fs, float* red, const int tid, const GroupSync gs, const int t, const int head, __nv_bfloat16* out,
     int out_stride, const float* part_o, const float* part_ml, const int* token_pos, int nq, int hd, int splits,
-    int per, int window) {
+    int per, int window, int chunk = 0) {
     if (!ZLM_CHK(token_pos + t, 4)) return;
     const int pos = token_pos[t];
-    const int t_start = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int t_start = attn_first_key(pos, window, chunk);
     const int pages = pos / ZLM_PAGE + 1 - t_start / ZLM_PAGE;
     const int used = min(splits, (pages + per - 1) / per);
     const size_t base = ((size_t)t * nq + head) * splits;

@@ -7,6 +7,9 @@
 // query row, so a chunk of a prompt attends the earlier chunks exactly as a whole
 // prompt would.
 //
+// Options (AttnOpts, attn_common.cuh): keys of the query's own chunk of positions only, a tanh cap on the
+// scores, a sink per query head in the softmax's denominator, several key heads on one value head.
+//
 // Formula: s_t = (q . k_t) / sqrt(hd) for t in [t_start, pos], softmax, o = sum
 // p_t v_t (src/kernels/transformer/attention.zig:86-164); per-row bound in block
 // prefill: src/runtime/executor.zig:565-584; window start: :93-98.
@@ -25,7 +28,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
                          const int* __restrict__ block_table, int table_stride,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, int tiles_per_seq, int nq, int nkv,
-                         float scale_log2, int window, int sink) {
+                         float scale_log2, int window, int sink, AttnOpts opt) {
     constexpr int KS = HD / 16;
     constexpr int VS = VD / 16;
     constexpr int CH = HD / 8;
@@ -48,8 +51,10 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
     const int kvh = head / (nq / nkv);
     const int start = seq_start[r];
     const int* pages = block_table + (size_t)seq_slot[r] * table_stride;
-    const size_t page_stride = (size_t)2 * nkv * TILE;
-    const size_t v_off = (size_t)nkv * TILE;
+    const size_t page_stride = (size_t)(nkv + nkv / opt.v_share) * TILE;
+    const size_t v_off = (size_t)(nkv - kvh + kvh / opt.v_share) * TILE;      // from this key head to its value head
+    const int chunk = opt.chunk;
+    const float softcap = opt.softcap;
 
     // positions of this thread's two rows; rows beyond the tile's tokens are idle
     const int i0 = warp * 16 + g, i1 = i0 + 8;
@@ -62,15 +67,15 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
           ZLM_CHK(out + (size_t)(tok0 + row0 + i1) * out_stride + (size_t)head * HD, HD * 2);
 #endif
     const int pos0 = start + row0 + i0, pos1 = start + row0 + i1;
-    const int lo0 = (window != 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
-    const int lo1 = (window != 0 && pos1 + 1 > window) ? pos1 + 1 - window : 0;
+    const int lo0 = attn_first_key(pos0, window, chunk), lo1 = attn_first_key(pos1, window, chunk);
     // keys the block and this warp can need
     const int blk_first = start + row0, blk_last = start + row0 + rows - 1;
-    const int blk_lo = (window != 0 && blk_first + 1 > window) ? blk_first + 1 - window : 0;
+    const int blk_lo = attn_first_key(blk_first, window, chunk);
     const int page_lo = blk_lo / ZLM_PAGE, page_hi = blk_last / ZLM_PAGE + 1;
     const int w_first = start + row0 + warp * 16;
     const int w_last = min(blk_last, w_first + 15);
-    const int w_lo = (window != 0 && w_first + 1 > window) ? w_first + 1 - window : 0;
+    const int w_lo = attn_first_key(w_first, window, chunk);
+    const int w_last_lo = attn_first_key(w_last, window, chunk);        // (a row's first key does not fall as positions grow)
     const bool warp_idle = warp * 16 >= rows;
 
     unsigned qf[KS][4];
@@ -92,8 +97,8 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    if (sink) {          // a key of score 0 without a value: one more term in every row's sum
-        m0 = m1 = 0.f;
+    if (sink) {          // a key of score 0 (or sinks[head]) without a value: one more term in every row's sum
+        m0 = m1 = attn_sink_log2(opt.sinks, head);
         if (qd == 0) l0 = l1 = 1.f;
     }
 
@@ -134,15 +139,15 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
             for (int np = 0; np < 4; ++np) {           // pairs of key tiles
                 const int mi = lane >> 3;
                 const int row = np * 16 + (mi >> 1) * 8 + (lane & 7);
-                const int chunk = ks * 2 + (mi & 1);
+                const int col = ks * 2 + (mi & 1);
                 unsigned b00, b01, b10, b11;
-                dec_ldsm4(b00, b01, b10, b11, kt + tile_off<HD>(row, chunk));
+                dec_ldsm4(b00, b01, b10, b11, kt + tile_off<HD>(row, col));
                 dec_mma(s[2 * np], qf[ks], b00, b01);
                 dec_mma(s[2 * np + 1], qf[ks], b10, b11);
             }
         }
         // scale, mask by each row's own bounds, running maximum
-        const bool edge = kbase + ZLM_PAGE - 1 > w_first || kbase < ((window != 0) ? w_last + 1 - window : 0);
+        const bool edge = kbase + ZLM_PAGE - 1 > w_first || kbase < w_last_lo;
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
@@ -151,8 +156,8 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
                 const int key = kbase + nt * 8 + qd * 2 + e;
                 const bool a = !edge || (key <= pos0 && key >= lo0);
                 const bool c = !edge || (key <= pos1 && key >= lo1);
-                s[nt][e] = (a && ok0) ? s[nt][e] * scale_log2 : -INFINITY;
-                s[nt][2 + e] = (c && ok1) ? s[nt][2 + e] * scale_log2 : -INFINITY;
+                s[nt][e] = (a && ok0) ? attn_score_log2(s[nt][e], scale_log2, softcap) : -INFINITY;
+                s[nt][2 + e] = (c && ok1) ? attn_score_log2(s[nt][2 + e], scale_log2, softcap) : -INFINITY;
                 mx0 = fmaxf(mx0, s[nt][e]);
                 mx1 = fmaxf(mx1, s[nt][2 + e]);
             }
@@ -194,9 +199,9 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
             for (int dn = 0; dn < VS; ++dn) {
                 const int mi = lane >> 3;
                 const int row = kk * 16 + (mi & 1) * 8 + (lane & 7);
-                const int chunk = dn * 2 + (mi >> 1);
+                const int col = dn * 2 + (mi >> 1);
                 unsigned b0, b1, b2, b3;
-                dec_ldsm4t(b0, b1, b2, b3, vt + tile_off<HD>(row, chunk));
+                dec_ldsm4t(b0, b1, b2, b3, vt + tile_off<HD>(row, col));
                 dec_mma(o[2 * dn], pa, b0, b1);
                 dec_mma(o[2 * dn + 1], pa, b2, b3);
             }
@@ -229,7 +234,7 @@ template <int HD, int VD = HD>
 static int launch_prefill(__nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride,
                           const __nv_bfloat16* pool, const int* block_table, int table_stride,
                           const int* cu_seqlens, const int* seq_slot, const int* seq_start, int R, int max_new,
-                          int nq, int nkv, float scale, int window, int sink, cudaStream_t st) {
+                          int nq, int nkv, float scale, int window, int sink, AttnOpts opt, cudaStream_t st) {
     const size_t smem = (size_t)4 * ZLM_PAGE * HD * sizeof(__nv_bfloat16);
     auto kern = attention_prefill_kernel<HD, VD>;
     static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];
@@ -245,7 +250,7 @@ static int launch_prefill(__nv_bfloat16* out, int out_stride, const __nv_bfloat1
     ZLM_REQUIRE((long long)R * tiles < 2147483647LL && nq <= 65535, "attention_prefill: too many tiles");
     dim3 grid(R * tiles, nq);
     kern<<<grid, PRE_THREADS, smem, st>>>(out, out_stride, q, q_stride, pool, block_table, table_stride, cu_seqlens,
-                                         seq_slot, seq_start, tiles, nq, nkv, scale * 1.4426950408889634f, window, sink);
+                                         seq_slot, seq_start, tiles, nq, nkv, scale * 1.4426950408889634f, window, sink, opt);
     return zlm_check_launch("attention_prefill");
 }
 
@@ -258,17 +263,21 @@ extern "C" int zlm_attention_prefill_supported(int nq, int nkv, int hd) {
 extern "C" int zlm_attention_prefill(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                      const int* block_table, int table_stride, const int* cu_seqlens,
                                      const int* seq_slot, const int* seq_start, int R, int max_new, int nq,
-                                     int nkv, int hd, float scale, int window, int sink, cudaStream_t st) {
+                                     int nkv, int hd, float scale, int window, int sink, int chunk, float softcap,
+                                     const float* sinks, int v_share, cudaStream_t st) {
     if (R == 0 || max_new == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_attention_prefill_supported(nq, nkv, hd),
                 "attention_prefill: %d heads over %d kv heads of size %d is not a shape this kernel takes", nq, nkv, hd);
+    ZLM_REQUIRE(chunk >= 0 && softcap >= 0.f && v_share >= 1 && nkv % v_share == 0,
+                "attention_prefill: chunk=%d softcap=%g v_share=%d", chunk, (double)softcap, v_share);
+    const AttnOpts opt{chunk, softcap, sinks, v_share};
     ZLM_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0),
                 "attention_prefill: q and out must be 4-byte aligned");
 #define ZLM_PRE_CASE(H)                                                                                         \
     case H:                                                                                                     \
         return launch_prefill<H>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,            \
                                  (const __nv_bfloat16*)pool, block_table, table_stride, cu_seqlens, seq_slot,   \
-                                 seq_start, R, max_new, nq, nkv, scale, window, sink, st);
+                                 seq_start, R, max_new, nq, nkv, scale, window, sink, opt, st);
     switch (hd) {
         ZLM_PRE_CASE(16) ZLM_PRE_CASE(32) ZLM_PRE_CASE(48) ZLM_PRE_CASE(64) ZLM_PRE_CASE(80) ZLM_PRE_CASE(96)
         ZLM_PRE_CASE(112) ZLM_PRE_CASE(128) ZLM_PRE_CASE(144) ZLM_PRE_CASE(160) ZLM_PRE_CASE(176) ZLM_PRE_CASE(192)
@@ -288,17 +297,21 @@ extern "C" int zlm_attention_prefill_vd_supported(int nq, int nkv, int hd, int v
 extern "C" int zlm_attention_prefill_vd(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                         const int* block_table, int table_stride, const int* cu_seqlens,
                                         const int* seq_slot, const int* seq_start, int R, int max_new, int nq,
-                                        int nkv, int hd, int vd, float scale, int window, int sink, cudaStream_t st) {
+                                        int nkv, int hd, int vd, float scale, int window, int sink, int chunk,
+                                        float softcap, const float* sinks, int v_share, cudaStream_t st) {
     if (R == 0 || max_new == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_attention_prefill_vd_supported(nq, nkv, hd, vd),
                 "attention_prefill: keys of %d with values of %d columns is not a pair this kernel is built for", hd, vd);
+    ZLM_REQUIRE(chunk >= 0 && softcap >= 0.f && v_share >= 1 && nkv % v_share == 0,
+                "attention_prefill: chunk=%d softcap=%g v_share=%d", chunk, (double)softcap, v_share);
+    const AttnOpts opt{chunk, softcap, sinks, v_share};
     ZLM_REQUIRE(q_stride % 2 == 0 && out_stride % 2 == 0 && ((uintptr_t)q % 4 == 0) && ((uintptr_t)out % 4 == 0),
                 "attention_prefill: q and out must be 4-byte aligned");
 #define ZLM_PRE_VD(H, V)                                                                                           \
     if (hd == H && vd == V)                                                                                        \
         return launch_prefill<H, V>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,            \
                                     (const __nv_bfloat16*)pool, block_table, table_stride, cu_seqlens, seq_slot,   \
-                                    seq_start, R, max_new, nq, nkv, scale, window, sink, st);
+                                    seq_start, R, max_new, nq, nkv, scale, window, sink, opt, st);
     ZLM_PRE_VD(192, 128) ZLM_PRE_VD(128, 64) ZLM_PRE_VD(96, 64) ZLM_PRE_VD(64, 32) ZLM_PRE_VD(48, 32) ZLM_PRE_VD(32, 16)
 #undef ZLM_PRE_VD
     ZLM_REQUIRE(false, "attention_prefill: head_dim=%d values=%d", hd, vd);

@@ -22,11 +22,16 @@
 // A sequence with an odd number of pages loads its last page twice; the second copy's keys
 // lie beyond every row's position and are masked.  Every wait is bounded (see gemm_tcgen05.cu).
 //
+// Options (AttnOpts, attn_common.cuh): keys of the query's own chunk of positions only; a tanh cap on the scores
+// (tanh through one exponential and one reciprocal of the special-function unit, so a capped step costs the softmax
+// warps three such operations a score instead of one); a sink per query head; several key heads on one value head.
+//
 // Formula: s_t = (q . k_t) / sqrt(hd) for t in [t_start, pos], softmax, o = sum p_t v_t
 // (src/kernels/transformer/attention.zig:86-164; per-row bound in block prefill:
 // src/runtime/executor.zig:565-584; window start: :93-98).
 #define TC_FAMILY 2
 #include "tc_common.cuh"
+#include "attn_common.cuh"
 #include <math.h>
 
 #define FA_BM 128          // query rows per block
@@ -41,6 +46,14 @@ __device__ __forceinline__ float fa_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
     return y;
+}
+// a raw score as a capped base-2 exponent: k_out * tanh(y), y = s * scale / softcap, with k_in = 2 * scale *
+// log2(e) / softcap (so that 2^(s * k_in) = e^{2y}) and k_out = softcap * log2(e); tanh(y) = 1 - 2 / (e^{2y} + 1).
+// A masked score (-inf) stays -inf.
+__device__ __forceinline__ float fa_cap(float s, float k_in, float k_out) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;\n" : "=f"(r) : "f"(fa_ex2(s * k_in) + 1.0f));
+    return s == -INFINITY ? -INFINITY : fmaf(-2.0f * k_out, r, k_out);
 }
 __device__ __forceinline__ unsigned fa_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -92,13 +105,14 @@ __device__ __forceinline__ void fa_commit(uint64_t* bar) {
         "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <int HPC>
+// CAP: built with the cap on the scores (the form without it keeps the plain softmax's registers)
+template <int HPC, bool CAP>
 __global__ void __launch_bounds__(FA_THREADS(HPC), 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, int R, int tiles_per_seq, int nq, int nkv,
-                            float scale_log2, int window, int sink) {
+                            float scale_log2, int window, int sink, AttnOpts opt) {
     constexpr int KST = HPC == 2 ? 1 : 2;                           // stages of keys and of values: what fits beside
     constexpr int VST = HPC == 2 ? 2 : 3;                           // the Q and P tiles (7 tiles of 32 KB in all)
     constexpr unsigned Q_BYTES = FA_BM * FA_HD * 2;                 // two halves of [128][64]
@@ -150,7 +164,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int start = seq_start[r];
     const int* pages = block_table + (size_t)seq_slot[r] * table_stride;
     const int first_pos = start + row0, last_pos = start + row0 + rows - 1;
-    const int blk_lo = (window != 0 && first_pos + 1 > window) ? first_pos + 1 - window : 0;
+    const int blk_lo = attn_first_key(first_pos, window, opt.chunk);
+    const int last_lo = attn_first_key(last_pos, window, opt.chunk);        // (a row's first key does not fall as positions grow)
+    const int page_heads = nkv + nkv / opt.v_share;                         // heads of [64][128] in a page: keys, then values
     const int page_lo = blk_lo / ZLM_PAGE, page_hi = last_pos / ZLM_PAGE + 1;
     const int NP = page_hi - page_lo;
     const int NS = (NP + 1) / 2;               // steps of two pages
@@ -171,7 +187,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int pg = 0; pg < 2; ++pg) {
             // K: [half][page][64 keys][64 dims]: the 128 keys of a half are one operand tile
-            const int krow = ((page[pg] * 2 + 0) * nkv + kvh) * ZLM_PAGE;
+            const int krow = (page[pg] * page_heads + kvh) * ZLM_PAGE;
             tma_load_2d(sK + sk * KV_BYTES + pg * (PAGE_BYTES / 2), &map_kv, 0, krow, &k_full[sk]);
             tma_load_2d(sK + sk * KV_BYTES + KV_BYTES / 2 + pg * (PAGE_BYTES / 2), &map_kv, 64, krow, &k_full[sk]);
         }
@@ -181,7 +197,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
         for (int pg = 0; pg < 2; ++pg) {
             // V: [page][half][64 keys][64 dims]
-            const int vrow = ((page[pg] * 2 + 1) * nkv + kvh) * ZLM_PAGE;
+            const int vrow = (page[pg] * page_heads + nkv + kvh / opt.v_share) * ZLM_PAGE;
             tma_load_2d(sV + sv * KV_BYTES + pg * PAGE_BYTES, &map_kv, 0, vrow, &v_full[sv]);
             tma_load_2d(sV + sv * KV_BYTES + pg * PAGE_BYTES + PAGE_BYTES / 2, &map_kv, 64, vrow, &v_full[sv]);
         }
@@ -292,10 +308,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const int i = lg * 32 + lane;                   // row of the tile = lane of tensor memory
         const bool row_ok = i < rows;
         const int pos = start + row0 + i;
-        const int lo = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+        const int lo = attn_first_key(pos, window, opt.chunk);
         const unsigned lane_addr = (unsigned)(lg * 32) << 16;
-        // (sink: a key of score 0 without a value, one more term in the row's sum)
-        float m_ref = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+        // (sink: a key of score 0, or sinks[head], without a value, one more term in the row's sum)
+        float m_ref = sink ? attn_sink_log2(opt.sinks, head) : -INFINITY, l = sink ? 1.f : 0.f;
+        constexpr bool capped = CAP;
+        const float k_in = capped ? 2.0f * scale_log2 / opt.softcap : 0.f, k_out = opt.softcap * 1.4426950408889634f;
         bool ok = true;
         for (int j = 0; j < NS; ++j) {
             ok = mbar_wait_warp(&s_full[hh], j & 1, abort_flag, 3);
@@ -303,8 +321,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             if (!ok || *abort_flag) { ok = false; break; }
             const int kbase = (page_lo + 2 * j) * ZLM_PAGE;
             // a step that every row of the tile sees whole needs no mask (block-uniform test)
-            const bool inner = rows == FA_BM && kbase + FA_BK - 1 <= first_pos &&
-                               (window == 0 || kbase >= last_pos + 1 - window);
+            const bool inner = rows == FA_BM && kbase + FA_BK - 1 <= first_pos && kbase >= last_lo;
             // the row's 128 scores into registers in one round trip to tensor memory; then S is free
             float sv[FA_BK];
 #pragma unroll
@@ -327,7 +344,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     mx4[e & 3] = fmaxf(mx4[e & 3], sv[e]);
                 }
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // -inf stays -inf
+            // (the cap is monotonic too: the capped maximum is the maximum's cap)
+            const float mx_raw = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            const float mx = capped ? fa_cap(mx_raw, k_in, k_out) : mx_raw * scale_log2;          // -inf stays -inf
             // lazy reference: move it only when the maximum grew by more than 2^8
             const bool grow = mx > m_ref + FA_RESCALE;              // also true for the first real maximum
             const float m_new = grow ? mx : m_ref;
@@ -363,7 +382,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 float p[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    p[e] = fa_ex2(fmaf(sv[ch * 8 + e], scale_log2, -ref));
+                    p[e] = capped ? fa_ex2(fa_cap(sv[ch * 8 + e], k_in, k_out) - ref)
+                                  : fa_ex2(fmaf(sv[ch * 8 + e], scale_log2, -ref));
                     ps4[e & 3] += p[e];
                 }
                 uint4 pk;
@@ -440,18 +460,23 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
                                         const void* pool, long long pool_pages, const int* block_table,
                                         int table_stride, const int* cu_seqlens, const int* seq_slot,
                                         const int* seq_start, int R, int max_new, int nq, int nkv, int hd,
-                                        float scale, int window, int sink, cudaStream_t st) {
+                                        float scale, int window, int sink, int chunk, float softcap, const float* sinks,
+                                        int v_share, cudaStream_t st) {
     if (R == 0 || max_new == 0) return ZLM_OK;
+    ZLM_REQUIRE(chunk >= 0 && softcap >= 0.f && v_share >= 1 && nkv % v_share == 0,
+                "attention_prefill_tc: chunk=%d softcap=%g v_share=%d", chunk, (double)softcap, v_share);
+    const AttnOpts opt{chunk, softcap, sinks, v_share};
+    const long long page_heads = nkv + nkv / v_share;
     ZLM_REQUIRE(zlm_attention_prefill_tc_supported(nq, nkv, hd, q_stride, out_stride),
                 "attention_prefill_tc: %d heads over %d kv heads of size %d (strides %d, %d) is not a shape this kernel takes",
                 nq, nkv, hd, q_stride, out_stride);
     ZLM_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)pool % 16 == 0),
                 "attention_prefill_tc: q, out and the pool must be 16-byte aligned");
-    ZLM_REQUIRE(pool_pages * 2 * nkv * ZLM_PAGE < 2147483647LL, "attention_prefill_tc: the pool has too many rows for a tensor map coordinate");
+    ZLM_REQUIRE(pool_pages * page_heads * ZLM_PAGE < 2147483647LL, "attention_prefill_tc: the pool has too many rows for a tensor map coordinate");
     CUtensorMap mq, mkv;
     int rc = zlm_make_map_2d(&mq, q, T, nq * hd, q_stride, FA_BM, 64);
     if (rc) return rc;
-    rc = zlm_make_map_2d(&mkv, pool, pool_pages * 2 * nkv * ZLM_PAGE, hd, hd, ZLM_PAGE, 64);
+    rc = zlm_make_map_2d(&mkv, pool, pool_pages * page_heads * ZLM_PAGE, hd, hd, ZLM_PAGE, 64);
     if (rc) return rc;
     const int tiles = (max_new + FA_BM - 1) / FA_BM;
     const int hpc = zlm_attention_prefill_tc_heads(R, max_new, nq, nkv);
@@ -459,11 +484,11 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
     // seven tiles of 32 KB (Q and P per head, the K and V stages), barriers, and what is left of a kilobyte for rounding the base up
     size_t smem = (size_t)7 * FA_BK * FA_HD * 2 + 256 + 1024;
     if (smem > 232448) smem = 232448;
-#define ZLM_FA_LAUNCH(H)                                                                                          \
+#define ZLM_FA_LAUNCH(H, C)                                                                                       \
     {                                                                                                             \
         static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                     \
         if (!attr_set) {                                                                                          \
-            cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<H>,                                  \
+            cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<H, C>,                                  \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
             if (e != cudaSuccess) {                                                                               \
                 zlm_set_error("attention_prefill_tc: cannot reserve %zu bytes of shared memory: %s", smem,        \
@@ -472,12 +497,17 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
             }                                                                                                     \
             attr_set = true;                                                                                      \
         }                                                                                                         \
-        zlm_launch(attention_prefill_tc_kernel<H>, dim3(R * tiles * (nq / H)), dim3(FA_THREADS(H)), smem, st, mq, mkv,    \
+        zlm_launch(attention_prefill_tc_kernel<H, C>, dim3(R * tiles * (nq / H)), dim3(FA_THREADS(H)), smem, st, mq, mkv,    \
                    (__nv_bfloat16*)out, out_stride, block_table, table_stride, cu_seqlens, seq_slot, seq_start,   \
-                   R, tiles, nq, nkv, scale * 1.4426950408889634f, window, sink);                                       \
+                   R, tiles, nq, nkv, scale * 1.4426950408889634f, window, sink, opt);                                       \
     }
-    if (hpc == 2) ZLM_FA_LAUNCH(2)
-    else ZLM_FA_LAUNCH(1)
+    if (softcap > 0.f) {
+        if (hpc == 2) ZLM_FA_LAUNCH(2, true)
+        else ZLM_FA_LAUNCH(1, true)
+    } else {
+        if (hpc == 2) ZLM_FA_LAUNCH(2, false)
+        else ZLM_FA_LAUNCH(1, false)
+    }
 #undef ZLM_FA_LAUNCH
     return zlm_check_launch("attention_prefill_tc");
 }

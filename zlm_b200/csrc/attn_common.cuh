@@ -33,6 +33,42 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
     return *(unsigned*)&v;
 }
 
+// What a mixer may ask of the attention kernels beyond the scale and the window.
+//   chunk    > 0: a query sees only the keys of its own chunk of that many positions, counted from position 0
+//   softcap  > 0: scores become softcap * tanh(score * scale / softcap)
+//   sinks    one number per query head whose exponential joins the softmax's denominator without a value
+//            (null with the flag `sink` set: the number is 0)
+//   v_share  that many neighbouring key heads read one value head: a page is [nkv key heads | nkv / v_share value
+//            heads] of [ZLM_PAGE][hd] each (1: the ordinary [K | V] of nkv heads each)
+struct AttnOpts {
+    int chunk;
+    float softcap;
+    const float* sinks;
+    int v_share;
+};
+static inline AttnOpts attn_no_opts() { return AttnOpts{0, 0.f, nullptr, 1}; }
+
+// the first key that the query at `pos` reads
+__device__ __forceinline__ int attn_first_key(int pos, int window, int chunk) {
+    int lo = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    if (chunk > 0) lo = max(lo, pos - pos % chunk);
+    return lo;
+}
+
+// a raw dot product as a base-2 exponent: dot * scale * log2(e), capped first where the mixer asks for it
+// (tanh through one exponential: 1 - 2 / (e^{2x} + 1), absolute error of a few 1e-7 of the cap)
+__device__ __forceinline__ float attn_score_log2(float dot, float scale_log2, float softcap) {
+    if (softcap <= 0.f) return dot * scale_log2;
+    const float x = dot * scale_log2 / softcap;               // y = dot * scale / softcap = x / log2(e): e^{2y} = 2^{2x}
+    const float th = 1.0f - __fdividef(2.0f, exp2f(2.0f * x) + 1.0f);
+    return softcap * 1.4426950408889634f * th;
+}
+
+// the running maximum a row starts from (base-2 exponent) when the softmax has a sink
+__device__ __forceinline__ float attn_sink_log2(const float* sinks, int head) {
+    return (sinks && ZLM_CHK(sinks + head, 4)) ? sinks[head] * 1.4426950408889634f : 0.f;
+}
+
 // element offset of (row, 16-byte chunk) inside a [64][HD] tile; rows of 128 bytes
 // or more are swizzled so that ldmatrix reads 8 rows without bank conflicts
 template <int HD> __device__ __forceinline__ int tile_off(int row, int chunk) {

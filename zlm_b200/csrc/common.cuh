@@ -261,3 +261,11 @@ static inline void zlm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     zlm_count_launch();
     cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);     // errors surface in zlm_check_launch
 }
+
+// The products' gated modes: 3, silu(gate) * up, and 7, gelu_tanh(gate) * up, with
+// gelu_tanh(z) = 0.5 z (1 + tanh(c (z + 0.044715 z^3))) = z / (1 + e^{-2 c (z + 0.044715 z^3)}), c = sqrt(2 / pi)
+#define ZLM_GATED(M) ((M) == 3 || (M) == 7)
+template <int MODE> __device__ __forceinline__ float gated_mul(float g, float u) {
+    if (MODE == 7) return (g / (1.0f + expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)))) * u;
+    return (g / (1.0f + expf(-g))) * u;
+}

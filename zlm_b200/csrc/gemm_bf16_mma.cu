@@ -127,7 +127,7 @@ gemm_bf16_mma_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     cp_async_wait<0>();
 
     const int g = lane >> 2, q = lane & 3;
-    if constexpr (MODE == 3) {
+    if constexpr (ZLM_GATED(MODE)) {
         // n-tiles come in pairs: 8 gate channels, then the 8 matching up channels
 #pragma unroll
         for (int i = 0; i < MT; ++i)
@@ -144,7 +144,7 @@ gemm_bf16_mma_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                         const float gt = acc[i][j][half * 2 + e], up = acc[i][j + 1][half * 2 + e];
                         if (ZLM_CHK((__nv_bfloat16*)Y + (size_t)m * ldy + n / 2 + q * 2 + e, 2))
                             ((__nv_bfloat16*)Y)[(size_t)m * ldy + n / 2 + q * 2 + e] =
-                                __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * up);
+                                __float2bfloat16_rn(gated_mul<MODE>(gt, up));
                     }
                 }
             }
@@ -191,7 +191,8 @@ static int launch_mma(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, i
     if (mode == 0) ZLM_LAUNCH_MODE(0)
     else if (mode == 1) ZLM_LAUNCH_MODE(1)
     else if (mode == 2) ZLM_LAUNCH_MODE(2)
-    else ZLM_LAUNCH_MODE(3)
+    else if (mode == 3) ZLM_LAUNCH_MODE(3)
+    else ZLM_LAUNCH_MODE(7)
 #undef ZLM_LAUNCH_MODE
     return zlm_check_launch("gemm_bf16_mma");
 }
@@ -205,8 +206,8 @@ extern "C" int zlm_gemm_bf16_mma(void* Y, const void* X, const void* W, int T, i
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemm_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_bf16: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode >= 0 && mode <= 3, "gemm_bf16: mode %d", mode);
-    ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemm_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
+    ZLM_REQUIRE((mode >= 0 && mode <= 3) || mode == 7, "gemm_bf16: mode %d", mode);
+    ZLM_REQUIRE(!ZLM_GATED(mode) || N % 16 == 0, "gemm_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     if (T > 64) return launch_mma<128, 128, 2, 4>(Y, x, w, T, N, K, ldx, ldy, mode, st);

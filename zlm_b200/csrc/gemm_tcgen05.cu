@@ -31,7 +31,7 @@
 #define TC_FAMILY 1
 #include "tc_common.cuh"
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+// (the gated modes 3 and 7 and their activations: ZLM_GATED, gated_mul in common.cuh)
 
 // a thread's 16 consecutive outputs (columns n .. n+15) of token `row` in the wanted mode
 template <int MODE>
@@ -52,7 +52,7 @@ __device__ __forceinline__ void store_row16(const float* v, void* Y, int row, in
 #ifdef ZLM_BOUNDS_CHECK
     {
         const int cols = whole ? 16 : N - n;
-        const bool ok = MODE == 3 ? ZLM_CHK((__nv_bfloat16*)Y + (size_t)row * ldy + n / 2, 16)
+        const bool ok = ZLM_GATED(MODE) ? ZLM_CHK((__nv_bfloat16*)Y + (size_t)row * ldy + n / 2, 16)
                       : MODE == 0 ? ZLM_CHK((__nv_bfloat16*)Y + (size_t)row * ldy + n, cols * 2)
                                   : ZLM_CHK((float*)Y + (size_t)row * ldy + n, cols * 4);
         if (!ok) return;
@@ -60,17 +60,17 @@ __device__ __forceinline__ void store_row16(const float* v, void* Y, int row, in
 #endif
     __nv_bfloat162 t;
 #define ZLM_PK(a, b) (t = __floats2bfloat162_rn(a, b), *(unsigned*)&t)
-    if (MODE == 3) {
+    if (ZLM_GATED(MODE)) {
         __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)row * ldy + n / 2;
         if (whole && ((uintptr_t)y & 15) == 0) {
             uint4 p;
-            p.x = ZLM_PK(silu_mul(v[0], v[8]), silu_mul(v[1], v[9]));
-            p.y = ZLM_PK(silu_mul(v[2], v[10]), silu_mul(v[3], v[11]));
-            p.z = ZLM_PK(silu_mul(v[4], v[12]), silu_mul(v[5], v[13]));
-            p.w = ZLM_PK(silu_mul(v[6], v[14]), silu_mul(v[7], v[15]));
+            p.x = ZLM_PK(gated_mul<MODE>(v[0], v[8]), gated_mul<MODE>(v[1], v[9]));
+            p.y = ZLM_PK(gated_mul<MODE>(v[2], v[10]), gated_mul<MODE>(v[3], v[11]));
+            p.z = ZLM_PK(gated_mul<MODE>(v[4], v[12]), gated_mul<MODE>(v[5], v[13]));
+            p.w = ZLM_PK(gated_mul<MODE>(v[6], v[14]), gated_mul<MODE>(v[7], v[15]));
             *(uint4*)y = p;
         } else if (whole) {
-            for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(silu_mul(v[i], v[8 + i]));
+            for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(gated_mul<MODE>(v[i], v[8 + i]));
         }
     } else if (MODE == 0) {
         __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)row * ldy + n;
@@ -105,7 +105,7 @@ __device__ __forceinline__ void store_row16(const float* v, void* Y, int row, in
 // this thread's output `row`, tokens t0 .. t0+15, in the wanted mode; every lane of the warp calls it
 template <int MODE>
 __device__ __forceinline__ void store_swapped16(const float* v, void* Y, int row, int t0, int T, int N, int ldy, int lane) {
-    if (MODE == 3) {
+    if (ZLM_GATED(MODE)) {
         // lanes 0-7 and 16-23 hold gate channels, lanes 8-15 and 24-31 the matching up
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -113,7 +113,7 @@ __device__ __forceinline__ void store_swapped16(const float* v, void* Y, int row
             if ((lane & 8) == 0 && row < N && t0 + i < T) {
                 const int ch = (row >> 4) * 8 + (row & 7);
                 if (!ZLM_CHK((__nv_bfloat16*)Y + (size_t)(t0 + i) * ldy + ch, 2)) continue;
-                ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(silu_mul(v[i], u));
+                ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(gated_mul<MODE>(v[i], u));
             }
         }
         return;
@@ -607,7 +607,7 @@ __device__ __forceinline__ void qkv_epilogue_row(const QkvEpilogue& ep, unsigned
 // engine clips a box at the matrix's edges.  TCQ_BOX_ACC: accumulator columns that make a box.
 #define TCQ_RING 4
 #define TCQ_BOX_BYTES (32 * 64)
-#define TCQ_BOX_ACC(MODE) ((MODE) == 3 ? 64 : (MODE) == 0 ? 32 : 16)
+#define TCQ_BOX_ACC(MODE) (ZLM_GATED(MODE) ? 64 : (MODE) == 0 ? 32 : 16)
 #define TCQ_OUT_BYTES (4 * TCQ_RING * TCQ_BOX_BYTES)
 template <int BN, int STAGES, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
@@ -743,10 +743,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 constexpr int ACC = TCQ_BOX_ACC(MODE);
                 const unsigned taddr = tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC;
                 unsigned char* const ring = sOut + lg * (TCQ_RING * TCQ_BOX_BYTES);
-                const int n_out = MODE == 3 ? N / 2 : N;
+                const int n_out = ZLM_GATED(MODE) ? N / 2 : N;
 #pragma unroll 1
                 for (int c = 0; c < BN; c += ACC, ++boxes) {
-                    const int x = MODE == 3 ? (b0row + c) / 2 : b0row + c;
+                    const int x = ZLM_GATED(MODE) ? (b0row + c) / 2 : b0row + c;
                     if (x >= n_out || a0row + lg * 32 >= T) break;     // nothing of this box lies inside (warp-uniform)
                     // the box about to be overwritten was handed over TCQ_RING boxes ago: wait until
                     // the copy engine has read it (the later ones may still be on their way)
@@ -760,12 +760,12 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     for (int part = 0; part < ACC / 16; ++part) {
                         float v[16];
                         tc_ld16(taddr + (unsigned)(c + part * 16), v);
-                        if (MODE == 3) {
+                        if (ZLM_GATED(MODE)) {
                             uint4 pk;
-                            pk.x = ZLM_PK(silu_mul(v[0], v[8]), silu_mul(v[1], v[9]));
-                            pk.y = ZLM_PK(silu_mul(v[2], v[10]), silu_mul(v[3], v[11]));
-                            pk.z = ZLM_PK(silu_mul(v[4], v[12]), silu_mul(v[5], v[13]));
-                            pk.w = ZLM_PK(silu_mul(v[6], v[14]), silu_mul(v[7], v[15]));
+                            pk.x = ZLM_PK(gated_mul<MODE>(v[0], v[8]), gated_mul<MODE>(v[1], v[9]));
+                            pk.y = ZLM_PK(gated_mul<MODE>(v[2], v[10]), gated_mul<MODE>(v[3], v[11]));
+                            pk.z = ZLM_PK(gated_mul<MODE>(v[4], v[12]), gated_mul<MODE>(v[5], v[13]));
+                            pk.w = ZLM_PK(gated_mul<MODE>(v[6], v[14]), gated_mul<MODE>(v[7], v[15]));
                             *(uint4*)(row + ((part ^ sw) << 4)) = pk;
                         } else if (MODE == 0) {
                             uint4 p0, p1;
@@ -1007,9 +1007,9 @@ __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restr
     pdl_wait();
     const size_t total = (size_t)T * N;
     const int width = N - n_from;
-    const size_t count = (size_t)T * (MODE == 3 ? width / 2 : width);
+    const size_t count = (size_t)T * (ZLM_GATED(MODE) ? width / 2 : width);
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) {
-        if (MODE == 3) {
+        if (ZLM_GATED(MODE)) {
             // channel c of token t; its gate is output (c/8)*16 + c%8, its up 8 further
             const size_t t = e / (width / 2);
             const int c = n_from / 2 + (int)(e - t * (width / 2));
@@ -1019,7 +1019,7 @@ __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restr
                 !ZLM_CHK((__nv_bfloat16*)Y + t * ldy + c, 2))
                 continue;
             for (int s = 0; s < splits; ++s) { sg += part[s * total + g]; su += part[s * total + g + 8]; }
-            ((__nv_bfloat16*)Y)[t * ldy + c] = __float2bfloat16_rn(silu_mul(sg, su));
+            ((__nv_bfloat16*)Y)[t * ldy + c] = __float2bfloat16_rn(gated_mul<MODE>(sg, su));
         } else {
             const size_t t = e / width;
             const int n = n_from + (int)(e - t * width);
@@ -1038,13 +1038,14 @@ __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restr
 
 static int launch_reduce(void* Y, const float* scratch, int T, int N, int ldy, int mode, int splits, int n_from,
                          cudaStream_t st) {
-    const size_t elems = (size_t)T * (N - n_from) / (mode == 3 ? 2 : 1);
+    const size_t elems = (size_t)T * (N - n_from) / (ZLM_GATED(mode) ? 2 : 1);
     int blocks = (int)((elems + 255) / 256);
     if (blocks > 148 * 8) blocks = 148 * 8;
     if (mode == 0) zlm_launch(gemm_tc_reduce_kernel<0>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
     else if (mode == 1) zlm_launch(gemm_tc_reduce_kernel<1>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
     else if (mode == 2) zlm_launch(gemm_tc_reduce_kernel<2>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
-    else zlm_launch(gemm_tc_reduce_kernel<3>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    else if (mode == 3) zlm_launch(gemm_tc_reduce_kernel<3>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    else zlm_launch(gemm_tc_reduce_kernel<7>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
     return zlm_check_launch("gemm_tc_reduce");
 }
 
@@ -1144,6 +1145,7 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
     else if (kmode == 1) ZLM_TC_LAUNCH(1)
     else if (kmode == 2) ZLM_TC_LAUNCH(2)
     else if (kmode == 3) ZLM_TC_LAUNCH(3)
+    else if (kmode == 7) ZLM_TC_LAUNCH(7)
     else ZLM_TC_LAUNCH(4)
 #undef ZLM_TC_LAUNCH
     rc = zlm_check_launch("gemm_tc");
@@ -1190,7 +1192,8 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
     if (mode == 0) ZLM_TCP_LAUNCH(0)
     else if (mode == 1) ZLM_TCP_LAUNCH(1)
     else if (mode == 2) ZLM_TCP_LAUNCH(2)
-    else ZLM_TCP_LAUNCH(3)
+    else if (mode == 3) ZLM_TCP_LAUNCH(3)
+    else ZLM_TCP_LAUNCH(7)
 #undef ZLM_TCP_LAUNCH
     return zlm_check_launch("gemm_tc_persistent");
 }
@@ -1206,12 +1209,12 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
     if (rc) return rc;
     // the results go through the copy engine where the output's rows can be described to it
     // (16-byte aligned rows); else the threads store row by row
-    const int ybytes = (mode == 0 || mode == 3) ? 2 : 4;
-    const int y_tma = mode >= 0 && mode <= 3 && ((size_t)ldy * ybytes) % 16 == 0 && (uintptr_t)Y % 16 == 0 &&
-                      (mode != 3 || N % 2 == 0);
+    const int ybytes = (mode == 0 || ZLM_GATED(mode)) ? 2 : 4;
+    const int y_tma = ((mode >= 0 && mode <= 3) || mode == 7) && ((size_t)ldy * ybytes) % 16 == 0 && (uintptr_t)Y % 16 == 0 &&
+                      (!ZLM_GATED(mode) || N % 2 == 0);
     CUtensorMap my = mx;
     if (y_tma) {
-        rc = zlm_make_map_out(&my, Y, T, mode == 3 ? N / 2 : N, ldy, ybytes, 32, 64 / ybytes);
+        rc = zlm_make_map_out(&my, Y, T, ZLM_GATED(mode) ? N / 2 : N, ldy, ybytes, 32, 64 / ybytes);
         if (rc) return rc;
     }
     const size_t smem = (size_t)STAGES * (TC_BM + BN / 2) * TC_BK * 2 + TCQ_OUT_BYTES + 1024 + 256;
@@ -1237,7 +1240,8 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
     else if (mode == 5) {
         if constexpr (BN == 256 || BN == 128) ZLM_TCQ_LAUNCH(5)
     }
-    else ZLM_TCQ_LAUNCH(3)
+    else if (mode == 3) ZLM_TCQ_LAUNCH(3)
+    else ZLM_TCQ_LAUNCH(7)
 #undef ZLM_TCQ_LAUNCH
     return zlm_check_launch("gemm_tc_pair");
 }
@@ -1304,7 +1308,8 @@ static int launch_tc_few(void* Y, const void* X, const void* W, int T, int N, in
     if (mode == 0) ZLM_TCF_LAUNCH(0)
     else if (mode == 1) ZLM_TCF_LAUNCH(1)
     else if (mode == 2) ZLM_TCF_LAUNCH(2)
-    else ZLM_TCF_LAUNCH(3)
+    else if (mode == 3) ZLM_TCF_LAUNCH(3)
+    else ZLM_TCF_LAUNCH(7)
 #undef ZLM_TCF_LAUNCH
     rc = zlm_check_launch("gemm_tc_few");
     if (rc || plan.ks <= 1) return rc;
@@ -1394,15 +1399,16 @@ extern "C" int zlm_gemm_tc_tile_width(int T, int N, int K) {
 }
 
 // mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T;
-// mode 3: Y bf16 [T, N/2] = silu(gate) * up, W's rows in groups of 8 gate + 8 up (N a multiple of 16).
+// mode 3: Y bf16 [T, N/2] = silu(gate) * up, W's rows in groups of 8 gate + 8 up (N a multiple of 16);
+// mode 7: the same with gelu_tanh(gate).
 // scratch: zlm_gemm_tc_ksplit(T, N, K) * T * N floats if that number of shares is more than 1, else unused.
 extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
                            float* scratch, cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_gemm_tc_supported(T, N, K, ldx), "gemm_tc: shape T=%d N=%d K=%d (row stride %d) is not taken", T, N, K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode >= 0 && mode <= 3, "gemm_tc: mode %d", mode);
-    ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemm_tc: the fused gate/up product needs N=%d to be a multiple of 16", N);
+    ZLM_REQUIRE((mode >= 0 && mode <= 3) || mode == 7, "gemm_tc: mode %d", mode);
+    ZLM_REQUIRE(!ZLM_GATED(mode) || N % 16 == 0, "gemm_tc: the fused gate/up product needs N=%d to be a multiple of 16", N);
     const int ks = zlm_gemm_tc_ksplit(T, N, K);
     ZLM_REQUIRE(ks == 1 || scratch, "gemm_tc: scratch for %d shares of K is missing", ks);
     // few tokens: W is the 128-row operand so that it streams at full height

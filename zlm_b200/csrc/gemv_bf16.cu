@@ -195,7 +195,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         red[warp][j][g + 8][2 * q + 1] = acc[j][3];
     }
     __syncthreads();
-    if constexpr (MODE == 3) {
+    if constexpr (ZLM_GATED(MODE)) {
         for (int idx = tid; idx < NT * 8 * 8; idx += WARPS * 32) {
             const int j = idx / 64, rem = idx % 64;
             const int tok = j * 8 + rem / 8, row = rem % 8;
@@ -208,7 +208,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
             }
             if (nm.in_squares) { sg *= scale[tok]; su *= scale[tok]; }
             if (ZLM_CHK((__nv_bfloat16*)Y + (size_t)tok * ldy + n0 / 2 + row, 2))
-                ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn((sg / (1.0f + expf(-sg))) * su);
+                ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn(gated_mul<MODE>(sg, su));
         }
     } else {
 #pragma unroll
@@ -317,6 +317,7 @@ static int launch_gemv_w(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W
     else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     else if (mode == 3) zlm_launch(gemv_bf16_kernel<NT, 3, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
+    else if (mode == 7) zlm_launch(gemv_bf16_kernel<NT, 7, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     else zlm_launch(gemv_bf16_kernel<NT, 4, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     return zlm_check_launch("gemv_bf16");
 }
@@ -351,8 +352,8 @@ static int gemv_entry(void* Y, const void* X, const void* W, int T, int N, int K
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemv_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemv_bf16: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode >= 0 && mode <= 4, "gemv_bf16: mode %d", mode);
-    ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemv_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
+    ZLM_REQUIRE((mode >= 0 && mode <= 4) || mode == 7, "gemv_bf16: mode %d", mode);
+    ZLM_REQUIRE(!ZLM_GATED(mode) || N % 16 == 0, "gemv_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
     ZLM_REQUIRE(mode != 4 || (nm.weight.p && nm.next && nm.squares), "gemv_bf16: the following norm's weight and outputs are missing");
     ZLM_REQUIRE(!nm.in_squares || nm.in_blocks > 0, "gemv_bf16: sums of squares of %d blocks", nm.in_blocks);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;

@@ -13,7 +13,9 @@
 //                 dealt round-robin), so no warp holds more than 16 x 16 NU accumulators
 // with an fp32 running maximum and sum per head.  Pages come by cp.async, two stages.  With more than
 // one split (decode steps) the (max, sum, O) of a split go to scratch and the decode attention's
-// combine kernel merges them in a fixed order.
+// combine kernel merges them in a fixed order.  Options: `chunk` (a query reads only the records of its own chunk of
+// that many positions, counted from position 0) and `sinks` (a number per head whose exponential joins the softmax's
+// denominator without a value).
 #include "common.cuh"
 #include "attn_common.cuh"
 
@@ -28,7 +30,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
                   const __nv_bfloat16* __restrict__ pool, const int* __restrict__ block_table, int table_stride,
                   const int* __restrict__ token_pos, const int* __restrict__ token_slot, int T, int H, int r, int dr,
                   float scale_log2, int window, int splits, int per, float* __restrict__ part_o,
-                  float* __restrict__ part_ml, int fresh) {
+                  float* __restrict__ part_ml, int fresh, int chunk, const float* __restrict__ sinks) {
     constexpr int GT = GW * 32;                  // threads of a group
     constexpr int NTK = 8 / GW;                  // score tiles (of 8 keys) a warp takes of a page
     constexpr int WK = 8 * NTK;                  // keys a warp takes of a page
@@ -56,7 +58,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
         my_pos = token_pos[my_t];
         my_slot = token_slot[my_t];
     }
-    const int my_start = (window != 0 && my_pos + 1 > window) ? my_pos + 1 - window : 0;
+    const int my_start = attn_first_key(my_pos, window, chunk);
 
     auto load_page = [&](const int* pages, int p, int stage) {
         if (!ZLM_CHK(pages + p, 4)) return;
@@ -75,6 +77,14 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;          // rows g and g + 8
+    if (sinks && split == 0) {
+        // exp(sinks[head]) joins the row's sum without a value, once per (token, head): every warp of the group
+        // starts from it as the running maximum, one lane of one warp counts it
+        const int h0 = htile * 16 + g, h1 = h0 + 8;
+        m0 = h0 < H ? attn_sink_log2(sinks, h0) : 0.f;
+        m1 = h1 < H ? attn_sink_log2(sinks, h1) : 0.f;
+        if (wq == 0 && qd == 0) l0 = l1 = 1.f;
+    }
     bool q_loaded = false, waited = false;
 
     // the block's tokens, one run of equal slots after the other (a decode step: one token, one run)
@@ -85,8 +95,7 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
         int lo = 0x7fffffff, hi = -1;
         for (int i = lead; i < QT && t0 + i < T && token_slot[t0 + i] == slot; ++i) {
             const int p = token_pos[t0 + i];
-            const int s = (window != 0 && p + 1 > window) ? p + 1 - window : 0;
-            lo = min(lo, s);
+            lo = min(lo, attn_first_key(p, window, chunk));
             hi = max(hi, p);
         }
         const bool mine = have && my_slot == slot;
@@ -336,9 +345,9 @@ latent_mma_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const __nv_bf
 }
 
 // the decode attention's combine kernel (attention_decode.cu) merges the splits
-extern "C" int zlm_attention_decode_combine(void* out, int out_stride, const float* part_o, const float* part_ml,
-                                            const int* token_pos, int T, int nq, int hd, int splits, int per, int window,
-                                            cudaStream_t st);
+extern "C" int zlm_attention_decode_combine_chunk(void* out, int out_stride, const float* part_o, const float* part_ml,
+                                                  const int* token_pos, int T, int nq, int hd, int splits, int per,
+                                                  int window, int chunk, cudaStream_t st);
 
 static size_t latent_mma_smem(int D, int QT) {
     const size_t DS = D + LM_PAD, PS = ZLM_PAGE + LM_PAD;
@@ -369,7 +378,7 @@ template <int NU, int QT, int GW>
 static int launch_latent_mma(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                              const int* block_table, int table_stride, const int* token_pos, const int* token_slot,
                              int T, int H, int r, int dr, float scale, int window, int splits, int per, float* part_o,
-                             float* part_ml, int fresh, cudaStream_t st) {
+                             float* part_ml, int fresh, int chunk, const float* sinks, cudaStream_t st) {
     const size_t smem = latent_mma_smem(r + dr, QT);
     auto kern = latent_mma_kernel<NU, QT, GW>;
     static size_t reserved[64] = {};
@@ -385,11 +394,12 @@ static int launch_latent_mma(void* out, int out_stride, const void* q, int q_str
     dim3 grid((T + QT - 1) / QT, (H + 15) / 16, splits);
     zlm_launch(kern, grid, dim3(GW * 32 * QT), smem, st, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,
                (const __nv_bfloat16*)pool, block_table, table_stride, token_pos, token_slot, T, H, r, dr,
-               scale * 1.4426950408889634f, window, splits, per, part_o, part_ml, fresh);
+               scale * 1.4426950408889634f, window, splits, per, part_o, part_ml, fresh, chunk, sinks);
     int rc = zlm_check_launch("latent_attention_mma");
     if (rc) return rc;
     if (splits > 1)
-        rc = zlm_attention_decode_combine(out, out_stride, part_o, part_ml, token_pos, T, H, r, splits, per, window, st);
+        rc = zlm_attention_decode_combine_chunk(out, out_stride, part_o, part_ml, token_pos, T, H, r, splits, per, window,
+                                                chunk, st);
     return rc;
 }
 
@@ -399,8 +409,9 @@ extern "C" int zlm_latent_attention_mma(void* out, int out_stride, const void* q
                                         const int* block_table, int table_stride, const int* token_pos,
                                         const int* token_slot, int T, int H, int r, int dr, float scale, int window,
                                         int tokens_per_block, int splits, int per, float* part_o, float* part_ml,
-                                        int fresh, cudaStream_t st) {
+                                        int fresh, int chunk, const float* sinks, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(chunk >= 0, "latent_attention_mma: chunk=%d", chunk);
     ZLM_REQUIRE(zlm_latent_attention_mma_supported(H, r, dr), "latent_attention_mma: heads=%d kv_rank=%d rot_dim=%d is not a "
                 "shape this kernel takes", H, r, dr);
     ZLM_REQUIRE(splits >= 1 && splits <= 1024 && per >= 1 && (splits == 1 || tokens_per_block == 1),
@@ -414,7 +425,8 @@ extern "C" int zlm_latent_attention_mma(void* out, int out_stride, const void* q
     const int nu4 = ((r / 16) + 3) / 4, nu8 = ((r / 16) + 7) / 8;
 #define ZLM_LM(NU, QT, GW)                                                                                           \
     return launch_latent_mma<NU, QT, GW>(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,  \
-                                         token_slot, T, H, r, dr, scale, window, splits, per, part_o, part_ml, fresh, st)
+                                         token_slot, T, H, r, dr, scale, window, splits, per, part_o, part_ml, fresh, chunk, \
+                                         sinks, st)
 #define ZLM_LM_8(QT)                              \
     do {                                          \
         if (nu8 <= 1) ZLM_LM(1, QT, 8);           \

@@ -84,10 +84,11 @@ extern "C" int zlm_embed_scaled(float* out, const void* table, int dtype, float 
 
 // ---------------------------------------------------------------- norm of a sublayer's output, scale, residual add
 // One block per row; the block's size is a function of H alone, so the order of the sum of squares never depends on
-// the batch.  With H a multiple of 4 and up to 4 float4 a thread the row is read once.
+// the batch.  With H a multiple of 4 and up to 4 float4 a thread the row is read once.  `cast_out` (may be null)
+// receives the stream's new row rounded to bfloat16: what the next sublayer's products read.
 template <typename TY>
 __global__ void norm_scale_add_kernel(float* __restrict__ stream, const TY* __restrict__ y, VecW w, VecW ls, int has_ls,
-                                      int H, float eps) {
+                                      int H, float eps, __nv_bfloat16* __restrict__ cast_out) {
     __shared__ float red[32];
     pdl_trigger();
     const int r = blockIdx.x;
@@ -96,8 +97,10 @@ __global__ void norm_scale_add_kernel(float* __restrict__ stream, const TY* __re
     const TY* yr = y + (size_t)r * H;
     if (!ZLM_CHK(xr, (size_t)H * 4) || !ZLM_CHK(yr, (size_t)H * sizeof(TY)) ||
         !ZLM_CHK(w.p, (size_t)H * (w.dtype == ZLM_DTYPE_F32 ? 4 : 2)) ||
-        (has_ls && !ZLM_CHK(ls.p, (size_t)H * (ls.dtype == ZLM_DTYPE_F32 ? 4 : 2))))
+        (has_ls && !ZLM_CHK(ls.p, (size_t)H * (ls.dtype == ZLM_DTYPE_F32 ? 4 : 2))) ||
+        (cast_out && !ZLM_CHK(cast_out + (size_t)r * H, (size_t)H * 2)))
         return;
+    __nv_bfloat16* cr = cast_out ? cast_out + (size_t)r * H : nullptr;
     const int nv = H / 4;
     const bool in_regs = sizeof(TY) == 4 && H % 4 == 0 && nv <= NORM_MAX_V4 * (int)blockDim.x;
     float4 v[NORM_MAX_V4];
@@ -132,26 +135,31 @@ __global__ void norm_scale_add_kernel(float* __restrict__ stream, const TY* __re
                 a.x += ((v[j].x * inv) * wv.x) * l.x; a.y += ((v[j].y * inv) * wv.y) * l.y;
                 a.z += ((v[j].z * inv) * wv.z) * l.z; a.w += ((v[j].w * inv) * wv.w) * l.w;
                 *(float4*)(xr + i) = a;
+                if (cr) store4(cr + i, a.x, a.y, a.z, a.w);
             } else {
                 float4 a = *(float4*)(xr + i);
                 a.x += (v[j].x * inv) * wv.x; a.y += (v[j].y * inv) * wv.y;
                 a.z += (v[j].z * inv) * wv.z; a.w += (v[j].w * inv) * wv.w;
                 *(float4*)(xr + i) = a;
+                if (cr) store4(cr + i, a.x, a.y, a.z, a.w);
             }
         }
     } else {
         for (int i = threadIdx.x; i < H; i += blockDim.x) {
             float n = (to_f32(yr[i]) * inv) * w[i];
             if (has_ls) n *= ls[i];
-            xr[i] += n;
+            const float a = xr[i] + n;
+            xr[i] = a;
+            if (cr) cr[i] = __float2bfloat16_rn(a);
         }
     }
 }
 
 extern "C" int zlm_norm_scale_add(float* stream, const void* y, int y_dtype, const void* w, int w_dtype, const void* ls,
-                                  int ls_dtype, int R, int H, float eps, cudaStream_t st) {
+                                  int ls_dtype, int R, int H, float eps, void* cast_out, cudaStream_t st) {
     if (R == 0) return ZLM_OK;
     ZLM_REQUIRE(R > 0 && H > 0, "norm_scale_add: bad sizes R=%d H=%d", R, H);
+    ZLM_REQUIRE(H % 4 != 0 || (uintptr_t)cast_out % 8 == 0, "norm_scale_add: the bfloat16 copy must be 8-byte aligned");
     ZLM_REQUIRE(H % 4 != 0 || ((uintptr_t)stream % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)w % 16 == 0 &&
                                (uintptr_t)ls % 16 == 0),
                 "norm_scale_add: stream, input and vectors must be 16-byte aligned");
@@ -159,10 +167,11 @@ extern "C" int zlm_norm_scale_add(float* stream, const void* y, int y_dtype, con
     while (threads < 1024 && threads * 4 * NORM_MAX_V4 < H) threads *= 2;
     VecW vw{w, w_dtype}, vl{ls ? ls : w, ls ? ls_dtype : w_dtype};
     if (y_dtype == ZLM_DTYPE_F32)
-        zlm_launch(norm_scale_add_kernel<float>, R, threads, 0, st, stream, (const float*)y, vw, vl, ls ? 1 : 0, H, eps);
+        zlm_launch(norm_scale_add_kernel<float>, R, threads, 0, st, stream, (const float*)y, vw, vl, ls ? 1 : 0, H, eps,
+                   (__nv_bfloat16*)cast_out);
     else if (y_dtype == ZLM_DTYPE_BF16)
         zlm_launch(norm_scale_add_kernel<__nv_bfloat16>, R, threads, 0, st, stream, (const __nv_bfloat16*)y, vw, vl,
-                   ls ? 1 : 0, H, eps);
+                   ls ? 1 : 0, H, eps, (__nv_bfloat16*)cast_out);
     else
         ZLM_REQUIRE(false, "norm_scale_add: unsupported input dtype %d", y_dtype);
     return zlm_check_launch("norm_scale_add");

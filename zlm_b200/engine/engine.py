@@ -54,7 +54,10 @@ class Engine:
         self.model.bind(tensors)
         pages = (int(max_tokens) + PAGE_TOKENS - 1) // PAGE_TOKENS
         self.max_tokens = pages * PAGE_TOKENS
-        self.max_seq_len = int(min(max_seq_len or self.spec.max_position, self.spec.max_position, self.max_tokens))
+        # the longest sequence: what the caller says (a sequence may be longer than the cache where every layer gives
+        # pages back behind a window or a chunk), else no longer than the cache
+        self.max_seq_len = int(min(max_seq_len, self.spec.max_position) if max_seq_len
+                               else min(self.spec.max_position, self.max_tokens))
         self.max_batch = int(max_batch or min(pages, 256))
         self.cache = KVCache(self.spec.schedule, self.model.cache_requests(), self.model.state_requests(),
                              self.max_tokens, self.max_batch, self.max_seq_len, dtype, self.device,

@@ -19,6 +19,7 @@ PAGE_TOKENS = 64
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 STORE, ACCUM, STORE_F32, SWIGLU = 0, 1, 2, 3
+GATED_GELU = 7      # as SWIGLU with gelu_tanh(gate) instead of silu(gate)
 
 
 class KernelError(RuntimeError):
@@ -169,6 +170,7 @@ class CudaKernels:
         self._lazy_ok = False          # the next norm's output is read by products only (the arrangement's word)
         self._lazy = None              # (out, stream, weight, eps, rows times weight, sums of squares, blocks): a norm not run
         self._blank = None             # a tensor that is to be taken as zeros (see expect_blank)
+        self.gated_activations = ("silu", "gelu_tanh")      # what linear_swiglu's ``act`` takes
         self._scratch = {}
         self.scratch_generation = 0
         self._launches = 0
@@ -531,15 +533,17 @@ class CudaKernels:
         if self.lib.zlm_attention_prefill_tc_set_heads(c_int(heads)) != 0:
             raise KernelError(self.lib.zlm_last_error().decode())
 
-    def linear_swiglu(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None) -> None:
-        """out[t, c] = silu(x[t] . gate_c) * (x[t] . up_c) in one pass over w (bf16).  w is
+    def linear_swiglu(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None,
+                      act: str = "silu") -> None:
+        """out[t, c] = act(x[t] . gate_c) * (x[t] . up_c) in one pass over w (bf16).  w is
         [2I, K] with the rows in groups of 16: 8 gate channels, then the 8 matching up
-        channels (``interleave_gate_up``); out is [T, I]."""
+        channels (``interleave_gate_up``); out is [T, I].  ``act``: "silu" or "gelu_tanh"."""
         T, K = x.shape
         N = w.shape[0]
         assert x.dtype == w.dtype == out.dtype == torch.bfloat16 and w.shape[1] == K and N % 16 == 0
         assert out.shape == (T, N // 2) and x.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
-        self._bf16_product(out, x, w, T, N, K, x.stride(0), out.stride(0), SWIGLU, impl)
+        self._bf16_product(out, x, w, T, N, K, x.stride(0), out.stride(0),
+                           {"silu": SWIGLU, "gelu_tanh": GATED_GELU}[act], impl)
 
     def rope_table(self, out: torch.Tensor, inv_freq: torch.Tensor, n_rot: int, token_pos: torch.Tensor) -> None:
         """out [2, n_rot/2, T] fp32: cos and sin of token_pos[t] * inv_freq[i], the step's rotation
@@ -647,9 +651,6 @@ class CudaKernels:
         assert v_share >= 1 and nkv % v_share == 0 and chunk >= 0 and softcap >= 0
         assert pool[0].numel() == (nkv + nkv // v_share) * PAGE_TOKENS * hd and pool.shape[-1] == hd
         extra = (c_int(chunk), c_float(softcap), self._p(sinks), c_int(v_share))
-        plain = chunk == 0 and softcap == 0 and sinks is None and v_share == 1
-        if not plain:
-            plan = None         # (the options above: the kernel for any shape)
         if (plan is not None and plan.is_decode and q.dtype == torch.bfloat16
                 and self.lib.zlm_attention_decode_supported(nq, nkv, hd)):
             if len_bucket is None:
@@ -667,7 +668,7 @@ class CudaKernels:
                        self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
                        c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits), c_int(per),
                        self._p(part_o), self._p(part_ml), c_int(max(1, int(getattr(plan, "max_new", 1) or 1))),
-                       sk, self._stream())
+                       sk, *extra, self._stream())
             return
         if (plan is not None and not plan.is_decode and q.dtype == torch.bfloat16
                 and getattr(plan, "cu_seqlens", None) is not None
@@ -680,7 +681,7 @@ class CudaKernels:
                            c_int(block_table.stride(0)), self._p(plan.cu_seqlens),
                            self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R),
                            c_int(plan.max_new), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window),
-                           sk, self._stream())
+                           sk, *extra, self._stream())
                 return
             if v_dim is not None and v_dim < hd and self.lib.zlm_attention_prefill_vd_supported(nq, nkv, hd, v_dim):
                 # values narrower than keys (their rows in the pool are padded to the keys' width): the padding is
@@ -688,14 +689,14 @@ class CudaKernels:
                 self._call("zlm_attention_prefill_vd", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
                            self._p(pool), self._p(block_table), c_int(block_table.stride(0)), self._p(plan.cu_seqlens),
                            self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R), c_int(plan.max_new), c_int(nq),
-                           c_int(nkv), c_int(hd), c_int(v_dim), c_float(scale), c_int(window), sk, self._stream())
+                           c_int(nkv), c_int(hd), c_int(v_dim), c_float(scale), c_int(window), sk, *extra, self._stream())
                 return
             self._call("zlm_attention_prefill", self._p(out), c_int(out.stride(0)),
                        self._p(q), c_int(q.stride(0)), self._p(pool),
                        self._p(block_table), c_int(block_table.stride(0)),
                        self._p(plan.cu_seqlens), self._p(plan.seq_slot),
                        self._p(plan.seq_start), c_int(plan.R), c_int(plan.max_new), c_int(nq),
-                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), sk, self._stream())
+                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), sk, *extra, self._stream())
             return
         self._call("zlm_attention_generic", self._p(out), c_int(out.stride(0)),
                    self._p(q), c_int(q.stride(0)), c_int(_dt(q)), self._p(pool),
@@ -866,15 +867,13 @@ class CudaKernels:
         key/value record per token that every head reads (q [T, heads * (kv_rank + rot_dim)]).  ``plan`` is
         the step's context: with it bf16 steps run on the tensor-core kernel where it takes the sizes (kv_rank
         and rot_dim multiples of 16); without it, in 32-bit, or with ``impl="plain"``, the plain kernel runs.
+        Both kernels have both options.
         ``sinks`` [heads] fp32: exp(sinks[h]) joins the softmax's denominator of head h, without a value.  ``chunk``:
         a query sees only the records of its own chunk of that many positions."""
         T = q.shape[0]
         D = kv_rank + rot_dim
         if sinks is not None:
             assert sinks.dtype == torch.float32 and sinks.shape == (heads,) and sinks.is_contiguous()
-        if chunk or sinks is not None:
-            impl = "plain"
-
         assert q.shape[1] == heads * D and out.shape == (T, heads * kv_rank) and q.dtype == out.dtype == pool.dtype
         assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
         assert tuple(pool.shape[1:]) == (PAGE_TOKENS, D)
@@ -903,7 +902,7 @@ class CudaKernels:
                        self._p(pool), self._p(block_table), c_int(block_table.stride(0)), self._p(token_pos),
                        self._p(token_slot), c_int(T), c_int(heads), c_int(kv_rank), c_int(rot_dim), c_float(scale),
                        c_int(window), c_int(qt), c_int(splits), c_int(per), self._p(part_o), self._p(part_ml),
-                       c_int(fresh), self._stream())
+                       c_int(fresh), c_int(chunk), self._p(sinks), self._stream())
             return
         self._call("zlm_latent_attention", self._p(out), c_int(out.stride(0)), self._p(q), c_int(q.stride(0)),
                    c_int(_dt(q)), self._p(pool), self._p(block_table), c_int(block_table.stride(0)),
@@ -932,15 +931,17 @@ class CudaKernels:
                    self._p(prev_state if pair is not None else None), c_int(T), c_int(H), c_int(table.shape[0]), self._stream())
 
     def norm_scale_add(self, stream: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float,
-                       layer_scale: Optional[torch.Tensor] = None) -> None:
-        """stream[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w (* layer_scale), in fp32; y fp32 or the compute dtype."""
+                       layer_scale: Optional[torch.Tensor] = None, cast_out: Optional[torch.Tensor] = None) -> None:
+        """stream[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w (* layer_scale), in fp32; y fp32 or the compute dtype.
+        ``cast_out`` (bfloat16, the stream's shape) receives the stream's new rows rounded once."""
         R, H = stream.shape
         assert stream.dtype == torch.float32 and y.shape == (R, H) and w.shape == (H,)
         assert stream.is_contiguous() and y.is_contiguous() and w.is_contiguous()
         assert layer_scale is None or (layer_scale.shape == (H,) and layer_scale.is_contiguous())
+        assert cast_out is None or (cast_out.dtype == torch.bfloat16 and cast_out.shape == (R, H) and cast_out.is_contiguous())
         self._call("zlm_norm_scale_add", self._p(stream), self._p(y), c_int(_dt(y)), self._p(w), c_int(_dt(w)),
                    self._p(layer_scale), c_int(_dt(layer_scale) if layer_scale is not None else F32), c_int(R), c_int(H),
-                   c_float(eps), self._stream())
+                   c_float(eps), self._p(cast_out), self._stream())
 
     def cast_rows(self, out: torch.Tensor, x: torch.Tensor) -> None:
         """out = x rounded to bfloat16 (x fp32, both contiguous and of one shape)."""

@@ -229,13 +229,15 @@ class Norm(Part):
     def forward(self, out: torch.Tensor, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
 
-    def add_into(self, stream: torch.Tensor, y: torch.Tensor) -> None:
+    def add_into(self, stream: torch.Tensor, y: torch.Tensor, cast_out: Optional[torch.Tensor] = None) -> bool:
         """stream += norm(y), in fp32, for arrangements that norm a sublayer's output (y fp32 [T, H]).  A norm with a
-        kernel for it overrides this; the default norms into scratch and adds."""
+        kernel for it overrides this; the default norms into scratch and adds.  ``cast_out``: a tensor of the compute
+        dtype that may receive the stream's new rows; the answer says whether it did."""
         out = self.rt.ws.get("norm.add_into", y.shape, torch.float32)
         self.forward(out, y)
         self.finish_products()
         stream.add_(out)
+        return False
 
 
 class PositionEncoding(Part):

@@ -49,6 +49,7 @@ class PreNormBlock(Part):
 
     def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
         rt = self.rt
+        ctx.extras.pop("stream.rounded", None)         # (this block changes the stream: a rounded copy of it is no longer one)
         x = rt.ws.get("block.normed", hidden.shape, rt.dtype)
         # What the kernel object may make of knowing who follows whom (``CudaKernels.expect_norm``): the
         # norm after a part, so that the part's last product can prepare it, and whether a norm's
@@ -102,14 +103,16 @@ class SublayerNormBlock(Part):
     def first_norm_weight(self):
         return None             # the block's first reader of the stream is not a norm
 
-    def _sublayer(self, part, norm: Norm, hidden: torch.Tensor, run) -> None:
+    def _sublayer(self, part, norm: Norm, hidden: torch.Tensor, run, ctx: StepContext) -> None:
         rt, k = self.rt, self.rt.k
         self.finish_products()          # (a block of another arrangement before this one may have left its last product)
         if rt.dtype == torch.float32:
             x = hidden
         else:
             x = rt.ws.get("block.input", hidden.shape, rt.dtype)
-            k.cast_rows(x, hidden)
+            # the norm that closed the sublayer before left the stream's rounded copy there (else: round it now)
+            if ctx.extras.pop("stream.rounded", None) != x.data_ptr():
+                k.cast_rows(x, hidden)
         y = rt.ws.get("block.sublayer_out", hidden.shape, torch.float32)
         blank = getattr(k, "expect_blank", None)
         if blank is not None:
@@ -119,13 +122,14 @@ class SublayerNormBlock(Part):
         run(x, y)
         if blank is not None:
             blank(None)
-        norm.add_into(hidden, y)
+        if norm.add_into(hidden, y, x if x is not hidden else None):
+            ctx.extras["stream.rounded"] = x.data_ptr()
 
     def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
         for word in ("expect_norm", "norm_output_read_by_products"):
             say = getattr(self.rt.k, word, None)
             if say is not None:
                 say(None if word == "expect_norm" else False)
-        self._sublayer(self.mixer, self.mixer_norm, hidden, lambda x, y: self.mixer.forward(x, y, ctx, io))
+        self._sublayer(self.mixer, self.mixer_norm, hidden, lambda x, y: self.mixer.forward(x, y, ctx, io), ctx)
         if not getattr(self.ffn, "is_identity", False):
-            self._sublayer(self.ffn, self.ffn_norm, hidden, lambda x, y: self.ffn.forward(x, y, ctx))
+            self._sublayer(self.ffn, self.ffn_norm, hidden, lambda x, y: self.ffn.forward(x, y, ctx), ctx)

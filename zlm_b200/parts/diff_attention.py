@@ -79,8 +79,10 @@ class DiffAttention(Mixer):
         # the decode kernel cuts the longest sequence's pages into parts (as for the other attention mixers)
         if not ctx.is_decode:
             return None
-        from ..kernels import attention_len_bucket
-        return ("gqa_attention", attention_len_bucket(ctx.max_len))
+        from ..kernels import PAGE_TOKENS, attention_len_bucket
+        # (with chunks a query's keys span a chunk's pages at most, however long the sequence)
+        reach = min(ctx.max_len, self.chunk + PAGE_TOKENS) if self.chunk else ctx.max_len
+        return ("gqa_attention", attention_len_bucket(reach))
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         # one fused projection: rows [q | k | v], with rows of zeros up to a multiple of 8

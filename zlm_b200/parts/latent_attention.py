@@ -93,8 +93,10 @@ class LatentAttention(Mixer):
         # captured step, holds for one rounded length
         if not ctx.is_decode:
             return None
-        from ..kernels import attention_len_bucket
-        return ("latent_attention", attention_len_bucket(ctx.max_len))
+        from ..kernels import PAGE_TOKENS, attention_len_bucket
+        # (with chunks a query's keys span a chunk's pages at most, however long the sequence)
+        reach = min(ctx.max_len, self.chunk + PAGE_TOKENS) if self.chunk else ctx.max_len
+        return ("latent_attention", attention_len_bucket(reach))
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         H, dn, dv, r = self.H, self.dn, self.dv, self.r

@@ -35,9 +35,9 @@ class SwiGLU(FeedForward):
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         gate, up = params.pop("gate_proj.weight"), params.pop("up_proj.weight")
         # bf16: gate and up rows interleaved in eights, so that the product's epilogue holds
-        # a channel's gate and up together and writes silu(gate) * up directly
-        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 8 == 0 and self.act == "silu"
-                      and hasattr(self.rt.k, "linear_swiglu"))
+        # a channel's gate and up together and writes act(gate) * up directly
+        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 8 == 0 and hasattr(self.rt.k, "linear_swiglu")
+                      and (self.act == "silu" or getattr(self.rt.k, "gated_activations", ()).count(self.act)))
         if self.fused:
             from ..kernels import interleave_gate_up
             self.w_gu = interleave_gate_up(gate, up)
@@ -60,7 +60,10 @@ class SwiGLU(FeedForward):
         T = x.shape[0]
         act = rt.ws.get("ffn.act", (T, self.inter), rt.dtype)
         if self.fused:
-            k.linear_swiglu(act, x, self.w_gu)
+            if self.act == "silu":
+                k.linear_swiglu(act, x, self.w_gu)
+            else:
+                k.linear_swiglu(act, x, self.w_gu, act=self.act)
         else:
             gu = rt.ws.get("ffn.gu", (T, 2 * self.inter), rt.dtype)
             k.linear(gu, x, self.w_gu)

@@ -130,6 +130,9 @@ class DecoderModel:
         residual stream [T, hidden].  ``embedding_io``: the embedding's per-sequence state, if it asked for any."""
         rt = self.rt
         hidden = rt.ws.get("model.hidden", (ctx.T, self.spec.hidden_size), torch.float32)
+        # (the embedding writes the stream anew: whatever a run before this one, with the same context, noted about
+        # copies of the stream, as the eager run before a capture does, no longer holds)
+        ctx.extras.pop("stream.rounded", None)
         if getattr(self.embedding, "uses_step", False):
             self.embedding.forward(hidden, ctx.token_ids, ctx, embedding_io)
         else:
@@ -143,6 +146,7 @@ class DecoderModel:
             ctx.extras["norm_after_block"] = first() if first is not None else None
             self.blocks[e.layer].forward(hidden, ctx, io)
         ctx.extras["norm_after_block"] = None
+        ctx.extras.pop("stream.rounded", None)
         return hidden
 
     def logits(self, hidden: torch.Tensor, rows: torch.Tensor, n_rows: int,

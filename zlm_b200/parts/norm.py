@@ -59,12 +59,15 @@ class RMSNorm(Norm):
             w = self._w_scaled
         self.rt.k.rmsnorm(out, x, w, self.eps, rows)
 
-    def add_into(self, stream: torch.Tensor, y: torch.Tensor) -> None:
+    def add_into(self, stream: torch.Tensor, y: torch.Tensor, cast_out: Optional[torch.Tensor] = None) -> bool:
         fused = getattr(self.rt.k, "norm_scale_add", None)
         if fused is None:
-            super().add_into(stream, y)
-            return
-        fused(stream, y, self.weight, self.eps, self.scale if self.layer_scale else None)
+            return super().add_into(stream, y)
+        if cast_out is None:
+            fused(stream, y, self.weight, self.eps, self.scale if self.layer_scale else None)
+            return False
+        fused(stream, y, self.weight, self.eps, self.scale if self.layer_scale else None, cast_out=cast_out)
+        return True
 
 
 @register_norm("none")

@@ -156,12 +156,12 @@ class ProfilingKernels:
         return self._timed(self._linear_name(w, "linear"), n, 2.0 * T * N * K, self.k.linear, out, x, w,
                            accumulate=accumulate, impl=impl, defer=defer and self.mode != "graph")
 
-    def linear_swiglu(self, out, x, w, impl=None):
+    def linear_swiglu(self, out, x, w, impl=None, **kw):
         T, K = x.shape
         N = w.shape[0]
         n = _nbytes(w) + T * K * x.element_size() + _nbytes(out)
         return self._timed(self._linear_name(w, "linear+swiglu"), n, 2.0 * T * N * K, self.k.linear_swiglu, out, x, w,
-                           impl=impl)
+                           impl=impl, **kw)
 
     def rope_table(self, out, inv_freq, n_rot, token_pos):
         return self._timed("rope_table", _nbytes(out), 0, self.k.rope_table, out, inv_freq, n_rot, token_pos)
@@ -180,22 +180,59 @@ class ProfilingKernels:
         return self._timed("qk_norm+rope+cache_write", n, 0, self.k.qk_norm_rope_write, qkv, q_w, k_w, eps, inv_freq,
                            n_rot, token_pos, token_slot, block_table, pool, nq, nkv, hd, write)
 
-    def attention(self, out, q, pool, block_table, token_pos, token_slot, nq, nkv, hd, scale, window, plan=None,
-                  len_bucket=None, v_dim=None, sink=False):
-        T, el = q.shape[0], q.element_size()
+    @staticmethod
+    def _reach(plan, window: int, chunk: int):
+        """(keys the step reads of the cache, query-key pairs it scores) from the step's host-side plan."""
+        def first(p):
+            lo = max(0, p + 1 - window) if window else 0
+            return max(lo, p - p % chunk) if chunk else lo
         keys_read, pairs = 0, 0
         if plan is not None and getattr(plan, "h_seq_start", None):
             for start, new in zip(plan.h_seq_start, plan.h_seq_new):
                 end = start + new
-                lo = max(0, start + 1 - window) if window else 0
-                keys_read += end - lo
+                keys_read += end - first(start)
                 for p in range(start, end):                 # visible keys of each new token
-                    pairs += (p + 1) - (max(0, p + 1 - window) if window else 0)
-        n = 2 * T * nq * hd * el + keys_read * 2 * nkv * hd * pool.element_size()
+                    pairs += (p + 1) - first(p)
+        return keys_read, pairs
+
+    def attention(self, out, q, pool, block_table, token_pos, token_slot, nq, nkv, hd, scale, window, plan=None,
+                  len_bucket=None, v_dim=None, sink=False, chunk=0, v_share=1, **kw):
+        T, el = q.shape[0], q.element_size()
+        keys_read, pairs = self._reach(plan, window, chunk)
+        n = 2 * T * nq * hd * el + keys_read * (nkv + nkv // v_share) * hd * pool.element_size()
         kind = "attention decode" if (plan is not None and plan.is_decode) else "attention prefill"
+        if v_share > 1:
+            kind += ", %d maps on one value head" % v_share
         return self._timed(kind, n, 2.0 * nq * (hd + (v_dim or hd)) * pairs, self.k.attention, out, q, pool, block_table,
                            token_pos, token_slot, nq, nkv, hd, scale, window, plan, len_bucket=len_bucket, v_dim=v_dim,
-                           sink=sink)
+                           sink=sink, chunk=chunk, v_share=v_share, **kw)
+
+    # differential attention and the stream of designs that norm a sublayer's output
+    def diff_prep(self, q_out, proj, *args, **kw):
+        T, el = proj.shape[0], proj.element_size()
+        n = T * proj.shape[1] * el + _nbytes(q_out) + T * (q_out.shape[1] // 2) * el
+        return self._timed("maps' qk_norm+rope+cache_write", n, 0, self.k.diff_prep, q_out, proj, *args, **kw)
+
+    def diff_combine(self, out, a, *args, **kw):
+        return self._timed("maps' difference+head norm", _nbytes(out) + _nbytes(a), 0, self.k.diff_combine, out, a, *args, **kw)
+
+    def norm_scale_add(self, stream, y, *args, **kw):
+        extra = _nbytes(kw.get("cast_out"))
+        return self._timed("sublayer norm+scale+add", 2 * _nbytes(stream) + _nbytes(y) + extra, 0, self.k.norm_scale_add,
+                           stream, y, *args, **kw)
+
+    def cast_rows(self, out, x):
+        return self._timed("stream to bf16", _nbytes(out) + _nbytes(x), 0, self.k.cast_rows, out, x)
+
+    def gated_act(self, out, gu, act="silu"):
+        return self._timed("gated activation", _nbytes(out) + _nbytes(gu), 0, self.k.gated_act, out, gu, act)
+
+    def head_scalar_gate(self, x, g):
+        T, H, V = x.shape
+        return self._timed("heads*gate", 2 * T * H * V * x.element_size(), 0, self.k.head_scalar_gate, x, g)
+
+    def embed_scaled(self, out, table, ids, *args, **kw):
+        return self._timed("embed", 2 * _nbytes(out), 0, self.k.embed_scaled, out, table, ids, *args, **kw)
 
     # short convolution, retention, gated heads
     def conv_norm_write(self, q_out, proj, conv_w, state, plan, block_table, pool, nq, nkv, dim, vdim, taps, norm, eps):
@@ -237,19 +274,13 @@ class ProfilingKernels:
         return self._timed(f"per-head linear [{w.shape[1]}x{w.shape[2]}]", n, 2.0 * T * w.numel(), self.k.head_linear, out, x, w)
 
     def latent_attention(self, out, q, pool, block_table, token_pos, token_slot, heads, kv_rank, rot_dim, scale,
-                         window=0, plan=None, len_bucket=None, impl=None):
-        keys_read, pairs = 0, 0
-        if plan is not None and getattr(plan, "h_seq_start", None):
-            for start, new in zip(plan.h_seq_start, plan.h_seq_new):
-                end = start + new
-                keys_read += end - (max(0, start + 1 - window) if window else 0)
-                for p in range(start, end):
-                    pairs += (p + 1) - (max(0, p + 1 - window) if window else 0)
+                         window=0, plan=None, len_bucket=None, impl=None, chunk=0, **kw):
+        keys_read, pairs = self._reach(plan, window, chunk)
         n = _nbytes(q) + _nbytes(out) + keys_read * (kv_rank + rot_dim) * pool.element_size()
         kind = "latent attention decode" if (plan is not None and plan.is_decode) else "latent attention prefill"
         return self._timed(kind, n, 2.0 * heads * (2 * kv_rank + rot_dim) * pairs, self.k.latent_attention, out, q, pool,
                            block_table, token_pos, token_slot, heads, kv_rank, rot_dim, scale, window, plan,
-                           len_bucket=len_bucket, impl=impl)
+                           len_bucket=len_bucket, impl=impl, chunk=chunk, **kw)
 
     def moe_route(self, idx, wgt, x, w_router, top, *args, **kw):
         T, K = x.shape
