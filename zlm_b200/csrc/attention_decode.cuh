@@ -135,14 +135,15 @@ __device__ __forceinline__ void attention_decode_item(
         }
         // scale (to base-2 exponent) and mask by position
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        attn_scores_log2<2>(s, scale_log2, softcap);
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = kbase + nt * 8 + qd * 2 + e;
                 const bool ok = key <= pos && key >= t_start;
-                s[nt][e] = ok ? attn_score_log2(s[nt][e], scale_log2, softcap) : -INFINITY;
-                s[nt][2 + e] = ok ? attn_score_log2(s[nt][2 + e], scale_log2, softcap) : -INFINITY;
+                s[nt][e] = ok ? s[nt][e] : -INFINITY;
+                s[nt][2 + e] = ok ? s[nt][2 + e] : -INFINITY;
                 mx0 = fmaxf(mx0, s[nt][e]);
                 mx1 = fmaxf(mx1, s[nt][2 + e]);
             }

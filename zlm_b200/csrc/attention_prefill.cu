@@ -149,6 +149,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
         // scale, mask by each row's own bounds, running maximum
         const bool edge = kbase + ZLM_PAGE - 1 > w_first || kbase < w_last_lo;
         float mx0 = -INFINITY, mx1 = -INFINITY;
+        attn_scores_log2<8>(s, scale_log2, softcap);
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
@@ -156,8 +157,8 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
                 const int key = kbase + nt * 8 + qd * 2 + e;
                 const bool a = !edge || (key <= pos0 && key >= lo0);
                 const bool c = !edge || (key <= pos1 && key >= lo1);
-                s[nt][e] = (a && ok0) ? attn_score_log2(s[nt][e], scale_log2, softcap) : -INFINITY;
-                s[nt][2 + e] = (c && ok1) ? attn_score_log2(s[nt][2 + e], scale_log2, softcap) : -INFINITY;
+                s[nt][e] = (a && ok0) ? s[nt][e] : -INFINITY;
+                s[nt][2 + e] = (c && ok1) ? s[nt][2 + e] : -INFINITY;
                 mx0 = fmaxf(mx0, s[nt][e]);
                 mx1 = fmaxf(mx1, s[nt][2 + e]);
             }

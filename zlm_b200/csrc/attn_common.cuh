@@ -64,6 +64,22 @@ __device__ __forceinline__ float attn_score_log2(float dot, float scale_log2, fl
     return softcap * 1.4426950408889634f * th;
 }
 
+// a tile's raw dot products as base-2 exponents, all at once: whether there is a cap is asked once (every thread of
+// a launch answers alike), so a kernel without one pays a multiplication a score and nothing else
+template <int NT> __device__ __forceinline__ void attn_scores_log2(float (&s)[NT][4], float scale_log2, float softcap) {
+    if (softcap > 0.f) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] = attn_score_log2(s[nt][e], scale_log2, softcap);
+    } else {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) s[nt][e] *= scale_log2;
+    }
+}
+
 // the running maximum a row starts from (base-2 exponent) when the softmax has a sink
 __device__ __forceinline__ float attn_sink_log2(const float* sinks, int head) {
     return (sinks && ZLM_CHK(sinks + head, 4)) ? sinks[head] * 1.4426950408889634f : 0.f;
