@@ -135,14 +135,17 @@ def make_attention_case(nq, nkv, hd, v_share, chunk, softcap, sink, lens, news, 
     return keys, values, q, pos, seq, starts, scale, sinks, row, first, group
 
 
-def run_attention_case(K, case, lens, news, probe, dtype, plan_of, seed=1):
+def run_attention_case(K, case, lens, news, probe, dtype, plan_of, seed=1, v_dim=None):
+    """``v_dim``: the values are that wide; the columns beyond them in the pool hold numbers that nobody may read, and
+    the output's columns beyond them must come out as zeros."""
     nq, nkv, hd, v_share, chunk, softcap, sink = case
     dt = DT[dtype]
     keys, values, q, pos, seq, starts, scale, sinks, row, first, group = make_attention_case(
         nq, nkv, hd, v_share, chunk, softcap, sink, lens, news, probe, dt, seed)
     slots = [3, 0, 5, 1, 4][:len(lens)]
     pool, table = shared_value_pool(keys, values, slots, 40, hd, seed)
-    want = torch.stack([plain_attention(q[t], keys[seq[t]], values[seq[t]], pos[t], scale, chunk, softcap,
+    vd = v_dim or hd
+    want = torch.stack([plain_attention(q[t], keys[seq[t]], values[seq[t]][..., :vd], pos[t], scale, chunk, softcap,
                                         sinks.double() if sinks is not None else None, group, v_share)
                         for t in range(len(pos))])
     T = len(pos)
@@ -151,16 +154,18 @@ def run_attention_case(K, case, lens, news, probe, dtype, plan_of, seed=1):
     K.attention(out, q.to(dt).view(T, nq * hd).cuda(), pool.to(dt).cuda(), table.cuda(),
                 torch.tensor(pos, dtype=torch.int32).cuda(), torch.tensor([slots[s] for s in seq], dtype=torch.int32).cuda(),
                 nq, nkv, hd, scale, 0, plan, chunk=chunk, softcap=softcap,
-                sinks=sinks.cuda() if sinks is not None else None, v_share=v_share)
+                sinks=sinks.cuda() if sinks is not None else None, v_share=v_share, v_dim=v_dim)
     assert K.gemm_tc_status() == 0
-    close(out.view(T, nq, hd), want, dtype, f"{case}", tol=3e-2 if dtype == "bfloat16" else None)
+    close(out.view(T, nq, hd)[..., :vd], want, dtype, f"{case}", tol=3e-2 if dtype == "bfloat16" else None)
+    assert not bool(out.view(T, nq, hd)[..., vd:].any()), f"{case}: the columns beyond the values are not zeros"
     # the key just inside holds the weight of the probe's last head (beside the sink, if any): its value comes out
     got = out.view(T, nq, hd)[row, nq - 1].double().cpu()
     share = 1.0
     if sinks is not None:
         s_in = softcap * math.tanh(30.0 / softcap) if softcap else 30.0
         share = 1.0 / (1.0 + math.exp(float(sinks[nq - 1]) - s_in))
-    v_in = values[0][first, (nkv - 1) // v_share] * share
+    v_in = values[0][first, (nkv - 1) // v_share][:vd] * share
+    got = got[:vd]
     assert float((got - v_in).abs().max()) <= 0.05 * float(v_in.abs().max()) + 0.05, f"{case}: the probe reads another key"
 
 
@@ -196,6 +201,20 @@ def test_attention_options_on_the_prompt_kernels(K, case, impl, probe):
         run_attention_case(K, case, LENS, NEWS, probe, "bfloat16", plan_of, seed=probe)
     finally:
         K.set_prefill_attention_heads(0)
+
+
+@pytest.mark.parametrize("impl", ["mma", None])
+@pytest.mark.parametrize("probe", [299, 256, 130])
+@pytest.mark.parametrize("case", [(5, 5, 192, 1, 0, 0.0, True), (4, 4, 192, 1, 100, 0.0, True), (3, 3, 192, 1, 0, 0.0, False),
+                                  (4, 2, 192, 1, 64, 30.0, False)])
+def test_keys_wider_than_values_on_the_prompt_kernels(K, case, impl, probe):
+    """Keys of 192 over values of 128 (what latent attention's whole prompts run on): the mma.sync kernel and, where
+    ``None`` lets the library choose, the tcgen05 kernel with three slabs of key dimensions."""
+    def plan_of(slots, starts, news):
+        plan = Plan(slots, starts, news)
+        plan.attention_impl = impl
+        return plan
+    run_attention_case(K, case, LENS, NEWS, probe, "bfloat16", plan_of, seed=probe + 1, v_dim=128)
 
 
 @pytest.mark.parametrize("blocks", [None, 8, 4000])

@@ -1,4 +1,5 @@
-// Prefill attention on the 5th-generation tensor cores, head size 128, bf16 paged cache.
+// Prefill attention on the 5th-generation tensor cores, bf16 paged cache: heads of 128, or keys of 192 with
+// values of 128 (KD: the keys are then three slabs of 64 dims where a head of 128 has two; one head a block).
 //
 // A block owns 128 query tokens of one sequence and HPC (1 or 2) query heads of one kv
 // group, and walks the keys these tokens may see in steps of 128 (two pages of the cache);
@@ -98,6 +99,19 @@ __device__ __forceinline__ void fa_issue_pv8(unsigned tmem_d, uint64_t pd, uint6
         "}\n"
         ::"r"(tmem_d), "l"(pd), "l"(vd), "r"(idesc), "r"(acc_first) : "memory");
 }
+// four more products of S: a third slab of 64 dims, 32 KB beyond the first in both operands (keys of 192)
+__device__ __forceinline__ void fa_issue_s4_more(unsigned tmem_d, uint64_t qd, uint64_t kd, unsigned idesc) {
+    asm volatile(
+        "{\n\t.reg .pred q, p1;\n\t.reg .b64 da, db;\n\t"
+        "elect.sync _|q, 0xffffffff;\n\t"
+        "setp.eq.b32 p1, 0, 0;\n\t"
+        "add.u64 da, %1, 2048;\n\tadd.u64 db, %2, 2048;\n\t@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p1;\n\t"
+        "add.u64 da, %1, 2050;\n\tadd.u64 db, %2, 2050;\n\t@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p1;\n\t"
+        "add.u64 da, %1, 2052;\n\tadd.u64 db, %2, 2052;\n\t@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p1;\n\t"
+        "add.u64 da, %1, 2054;\n\tadd.u64 db, %2, 2054;\n\t@q tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p1;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "l"(qd), "l"(kd), "r"(idesc) : "memory");
+}
 // an arrival at `bar` once the products issued so far have retired, from the same elected lane
 __device__ __forceinline__ void fa_commit(uint64_t* bar) {
     asm volatile(
@@ -106,27 +120,33 @@ __device__ __forceinline__ void fa_commit(uint64_t* bar) {
 }
 
 // CAP: built with the cap on the scores (the form without it keeps the plain softmax's registers)
-template <int HPC, bool CAP>
+// KD: the keys' and queries' width (128, or 192 with values of 128: rows of the pool and of q and out are KD wide)
+template <int HPC, bool CAP, int KD = FA_HD>
 __global__ void __launch_bounds__(FA_THREADS(HPC), 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
                             const int* __restrict__ seq_start, int R, int tiles_per_seq, int nq, int nkv,
                             float scale_log2, int window, int sink, AttnOpts opt) {
-    constexpr int KST = HPC == 2 ? 1 : 2;                           // stages of keys and of values: what fits beside
-    constexpr int VST = HPC == 2 ? 2 : 3;                           // the Q and P tiles (7 tiles of 32 KB in all)
-    constexpr unsigned Q_BYTES = FA_BM * FA_HD * 2;                 // two halves of [128][64]
+    static_assert((KD == 128 || KD == 192) && (KD == 128 || HPC == 1), "keys of 128, or of 192 with one head a block");
+    constexpr int NKH = KD / 64;                                    // slabs of 64 dims in a query or key row
+    constexpr int KST = (HPC == 2 || KD > 128) ? 1 : 2;             // stages of keys and of values: what fits beside
+    constexpr int VST = HPC == 2 ? 2 : 3;                           // the Q and P tiles (224 KB in all)
+    constexpr unsigned SLAB = FA_BM * 64 * 2;                       // [128 rows][64 dims]
+    constexpr unsigned Q_BYTES = NKH * SLAB;                        // slabs of [128][64]
     constexpr unsigned P_BYTES = FA_BM * FA_BK * 2;                 // two halves of [128 rows][64 keys]
-    constexpr unsigned PAGE_BYTES = ZLM_PAGE * FA_HD * 2;           // K or V of one page: two halves of [64][64]
-    constexpr unsigned KV_BYTES = 2 * PAGE_BYTES;                   // K or V of a step
-    static_assert(Q_BYTES / 2 == 16384 && P_BYTES / 2 == 16384 && KV_BYTES / 2 == 16384 && PAGE_BYTES == 16384,
+    constexpr unsigned PAGE_BYTES = ZLM_PAGE * FA_HD * 2;           // V of one page: two halves of [64][64]
+    constexpr unsigned KV_BYTES = 2 * PAGE_BYTES;                   // V of a step
+    constexpr unsigned K_BYTES = NKH * SLAB;                        // K of a step: slabs of [128 keys][64 dims]
+    static_assert(SLAB == 16384 && P_BYTES / 2 == 16384 && KV_BYTES / 2 == 16384 && PAGE_BYTES == 16384,
                   "the constants of the issue blocks");
+    static_assert(HPC * (Q_BYTES + P_BYTES) + KST * K_BYTES + VST * KV_BYTES <= 7 * 32768, "the tiles' shared memory");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = smem;                                       // [HPC] Q tiles
     unsigned char* sP = sQ + HPC * Q_BYTES;                         // [HPC] P tiles
-    unsigned char* sK = sP + HPC * P_BYTES;                         // [KST]: dims 0..63 of the 128 keys, then dims 64..127
-    unsigned char* sV = sK + KST * KV_BYTES;                        // [VST]: page 0 (two halves), page 1
+    unsigned char* sK = sP + HPC * P_BYTES;                         // [KST]: dims 0..63 of the 128 keys, then dims 64..127, ...
+    unsigned char* sV = sK + KST * K_BYTES;                         // [VST]: page 0 (two halves), page 1
     uint64_t* q_full = (uint64_t*)(sV + VST * KV_BYTES);
     uint64_t* k_full = q_full + 1;             // [KST]      TMA bytes landed
     uint64_t* k_empty = k_full + KST;          // [KST]      the heads' S = Q K^T of that step retired
@@ -183,13 +203,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         const int sk = j % KST, sv = j % VST;
         if (!mbar_wait(&k_empty[sk], ((j / KST) & 1) ^ 1, abort_flag, 1)) return false;
-        mbar_expect_tx(&k_full[sk], KV_BYTES);
+        mbar_expect_tx(&k_full[sk], K_BYTES);
 #pragma unroll
         for (int pg = 0; pg < 2; ++pg) {
-            // K: [half][page][64 keys][64 dims]: the 128 keys of a half are one operand tile
+            // K: [slab][page][64 keys][64 dims]: the 128 keys of a slab are one operand tile
             const int krow = (page[pg] * page_heads + kvh) * ZLM_PAGE;
-            tma_load_2d(sK + sk * KV_BYTES + pg * (PAGE_BYTES / 2), &map_kv, 0, krow, &k_full[sk]);
-            tma_load_2d(sK + sk * KV_BYTES + KV_BYTES / 2 + pg * (PAGE_BYTES / 2), &map_kv, 64, krow, &k_full[sk]);
+#pragma unroll
+            for (int sl = 0; sl < NKH; ++sl)
+                tma_load_2d(sK + sk * K_BYTES + sl * SLAB + pg * (SLAB / 2), &map_kv, 64 * sl, krow, &k_full[sk]);
         }
         k_issued = j + 1;
         if (!mbar_wait(&v_empty[sv], ((j / VST) & 1) ^ 1, abort_flag, 1)) return false;
@@ -224,9 +245,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         pdl_wait();
         mbar_expect_tx(q_full, HPC * Q_BYTES);
         for (int h = 0; h < HPC; ++h) {
-            // Q: two 64-column halves per head, 128 token rows
-            tma_load_2d(sQ + h * Q_BYTES, &map_q, (head0 + h) * FA_HD, tok0 + row0, q_full);
-            tma_load_2d(sQ + h * Q_BYTES + Q_BYTES / 2, &map_q, (head0 + h) * FA_HD + 64, tok0 + row0, q_full);
+            // Q: slabs of 64 columns per head, 128 token rows
+#pragma unroll
+            for (int sl = 0; sl < NKH; ++sl)
+                tma_load_2d(sQ + h * Q_BYTES + sl * SLAB, &map_q, (head0 + h) * KD + 64 * sl, tok0 + row0, q_full);
         }
         if (NS > 0) load_step(0);
     }
@@ -262,12 +284,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         auto issue_s = [&](int j) -> bool {
             const int s = j % KST;
             if (!mbar_wait_warp(&k_full[s], (j / KST) & 1, abort_flag, 2)) return false;
-            const uint64_t kd = make_desc(smem_u32(sK + s * KV_BYTES));
+            const uint64_t kd = make_desc(smem_u32(sK + s * K_BYTES));
 #pragma unroll
             for (int h = 0; h < HPC; ++h) {
                 if (j > 0 && !mbar_wait_warp(&s_empty[h], (j - 1) & 1, abort_flag, 5)) return false;
                 tc_fence_after();
                 fa_issue_s8(tmem_base + h * 256, make_desc(smem_u32(sQ + h * Q_BYTES)), kd, idesc_s);
+                if (KD > 128) fa_issue_s4_more(tmem_base + h * 256, make_desc(smem_u32(sQ + h * Q_BYTES)), kd, idesc_s);
                 fa_commit(&s_full[h]);
             }
             fa_commit(&k_empty[s]);                // the keys' stage is free when the heads' S have retired
@@ -400,7 +423,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         tc_fence_after();
         if (ok && !*abort_flag) {
             const float inv = row_ok ? 1.0f / l : 0.f;
-            __nv_bfloat16* orow = out + (size_t)(tok0 + row0 + i) * out_stride + (size_t)head * FA_HD;
+            __nv_bfloat16* orow = out + (size_t)(tok0 + row0 + i) * out_stride + (size_t)head * KD;
 #pragma unroll 1
             for (int c = 0; c < FA_HD; c += 16) {
                 float ov[16];
@@ -415,6 +438,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     *(uint4*)(orow + c + 8) = bq;
                 }
             }
+            // (out's rows are as wide as the keys: the columns beyond the values become zeros)
+            if (KD > FA_HD && row_ok && ZLM_CHK(orow + FA_HD, (KD - FA_HD) * 2)) {
+#pragma unroll
+                for (int c = FA_HD; c < KD; c += 8) *(uint4*)(orow + c) = make_uint4(0u, 0u, 0u, 0u);
+            }
         }
     }
     tc_fence_before();
@@ -428,6 +456,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
 extern "C" int zlm_attention_prefill_tc_supported(int nq, int nkv, int hd, int q_stride, int out_stride) {
     return (hd == FA_HD && nkv > 0 && nq % nkv == 0 && q_stride % 8 == 0 && out_stride % 8 == 0) ? 1 : 0;
+}
+// the same for keys of `hd` with values of `vd` columns (the rows of the pool, of q and of out are hd wide)
+extern "C" int zlm_attention_prefill_tc_vd_supported(int nq, int nkv, int hd, int vd, int q_stride, int out_stride) {
+    if (vd == hd) return zlm_attention_prefill_tc_supported(nq, nkv, hd, q_stride, out_stride);
+    return (hd == 192 && vd == FA_HD && nkv > 0 && nq % nkv == 0 && q_stride % 8 == 0 && out_stride % 8 == 0) ? 1 : 0;
 }
 
 // pool_rows: pages * 2 * nkv * 64 (all rows of the layer's pool, head size 128 each)
@@ -456,20 +489,21 @@ extern "C" int zlm_attention_prefill_tc_heads(int R, int max_new, int nq, int nk
     return two <= one ? 2 : 1;
 }
 
-extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q, int q_stride, int T,
-                                        const void* pool, long long pool_pages, const int* block_table,
-                                        int table_stride, const int* cu_seqlens, const int* seq_slot,
-                                        const int* seq_start, int R, int max_new, int nq, int nkv, int hd,
-                                        float scale, int window, int sink, int chunk, float softcap, const float* sinks,
-                                        int v_share, cudaStream_t st) {
+// vd: the values' columns (hd, or 128 under keys of 192: out's columns from vd on become zeros)
+extern "C" int zlm_attention_prefill_tc_vd(void* out, int out_stride, const void* q, int q_stride, int T,
+                                           const void* pool, long long pool_pages, const int* block_table,
+                                           int table_stride, const int* cu_seqlens, const int* seq_slot,
+                                           const int* seq_start, int R, int max_new, int nq, int nkv, int hd, int vd,
+                                           float scale, int window, int sink, int chunk, float softcap, const float* sinks,
+                                           int v_share, cudaStream_t st) {
     if (R == 0 || max_new == 0) return ZLM_OK;
     ZLM_REQUIRE(chunk >= 0 && softcap >= 0.f && v_share >= 1 && nkv % v_share == 0,
                 "attention_prefill_tc: chunk=%d softcap=%g v_share=%d", chunk, (double)softcap, v_share);
     const AttnOpts opt{chunk, softcap, sinks, v_share};
     const long long page_heads = nkv + nkv / v_share;
-    ZLM_REQUIRE(zlm_attention_prefill_tc_supported(nq, nkv, hd, q_stride, out_stride),
-                "attention_prefill_tc: %d heads over %d kv heads of size %d (strides %d, %d) is not a shape this kernel takes",
-                nq, nkv, hd, q_stride, out_stride);
+    ZLM_REQUIRE(zlm_attention_prefill_tc_vd_supported(nq, nkv, hd, vd, q_stride, out_stride),
+                "attention_prefill_tc: %d heads over %d kv heads of size %d, values of %d (strides %d, %d) is not a shape this kernel takes",
+                nq, nkv, hd, vd, q_stride, out_stride);
     ZLM_REQUIRE(((uintptr_t)q % 16 == 0) && ((uintptr_t)out % 16 == 0) && ((uintptr_t)pool % 16 == 0),
                 "attention_prefill_tc: q, out and the pool must be 16-byte aligned");
     ZLM_REQUIRE(pool_pages * page_heads * ZLM_PAGE < 2147483647LL, "attention_prefill_tc: the pool has too many rows for a tensor map coordinate");
@@ -479,16 +513,16 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
     rc = zlm_make_map_2d(&mkv, pool, pool_pages * page_heads * ZLM_PAGE, hd, hd, ZLM_PAGE, 64);
     if (rc) return rc;
     const int tiles = (max_new + FA_BM - 1) / FA_BM;
-    const int hpc = zlm_attention_prefill_tc_heads(R, max_new, nq, nkv);
+    const int hpc = hd > FA_HD ? 1 : zlm_attention_prefill_tc_heads(R, max_new, nq, nkv);
     ZLM_REQUIRE((long long)R * tiles * nq < 2147483647LL, "attention_prefill_tc: too many tiles");
     // seven tiles of 32 KB (Q and P per head, the K and V stages), barriers, and what is left of a kilobyte for rounding the base up
     size_t smem = (size_t)7 * FA_BK * FA_HD * 2 + 256 + 1024;
     if (smem > 232448) smem = 232448;
-#define ZLM_FA_LAUNCH(H, C)                                                                                       \
+#define ZLM_FA_LAUNCH(H, C, KD)                                                                                    \
     {                                                                                                             \
         static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                     \
         if (!attr_set) {                                                                                          \
-            cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<H, C>,                                  \
+            cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<H, C, KD>,                              \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
             if (e != cudaSuccess) {                                                                               \
                 zlm_set_error("attention_prefill_tc: cannot reserve %zu bytes of shared memory: %s", smem,        \
@@ -497,19 +531,33 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
             }                                                                                                     \
             attr_set = true;                                                                                      \
         }                                                                                                         \
-        zlm_launch(attention_prefill_tc_kernel<H, C>, dim3(R * tiles * (nq / H)), dim3(FA_THREADS(H)), smem, st, mq, mkv,    \
+        zlm_launch(attention_prefill_tc_kernel<H, C, KD>, dim3(R * tiles * (nq / H)), dim3(FA_THREADS(H)), smem, st, mq, mkv, \
                    (__nv_bfloat16*)out, out_stride, block_table, table_stride, cu_seqlens, seq_slot, seq_start,   \
                    R, tiles, nq, nkv, scale * 1.4426950408889634f, window, sink, opt);                                       \
     }
-    if (softcap > 0.f) {
-        if (hpc == 2) ZLM_FA_LAUNCH(2, true)
-        else ZLM_FA_LAUNCH(1, true)
+    if (hd > FA_HD) {
+        if (softcap > 0.f) ZLM_FA_LAUNCH(1, true, 192)
+        else ZLM_FA_LAUNCH(1, false, 192)
+    } else if (softcap > 0.f) {
+        if (hpc == 2) ZLM_FA_LAUNCH(2, true, FA_HD)
+        else ZLM_FA_LAUNCH(1, true, FA_HD)
     } else {
-        if (hpc == 2) ZLM_FA_LAUNCH(2, false)
-        else ZLM_FA_LAUNCH(1, false)
+        if (hpc == 2) ZLM_FA_LAUNCH(2, false, FA_HD)
+        else ZLM_FA_LAUNCH(1, false, FA_HD)
     }
 #undef ZLM_FA_LAUNCH
     return zlm_check_launch("attention_prefill_tc");
+}
+
+extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q, int q_stride, int T,
+                                        const void* pool, long long pool_pages, const int* block_table,
+                                        int table_stride, const int* cu_seqlens, const int* seq_slot,
+                                        const int* seq_start, int R, int max_new, int nq, int nkv, int hd,
+                                        float scale, int window, int sink, int chunk, float softcap, const float* sinks,
+                                        int v_share, cudaStream_t st) {
+    return zlm_attention_prefill_tc_vd(out, out_stride, q, q_stride, T, pool, pool_pages, block_table, table_stride,
+                                       cu_seqlens, seq_slot, seq_start, R, max_new, nq, nkv, hd, hd, scale, window, sink,
+                                       chunk, softcap, sinks, v_share, st);
 }
 
 // heads of a kv group per block: 0 lets the dispatcher choose; 1 or 2 force that many where the kv

@@ -683,6 +683,17 @@ class CudaKernels:
                            c_int(plan.max_new), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window),
                            sk, *extra, self._stream())
                 return
+            if (impl != "mma" and v_dim is not None and v_dim < hd
+                    and self.lib.zlm_attention_prefill_tc_vd_supported(nq, nkv, hd, v_dim, q.stride(0), out.stride(0))):
+                # keys of 192 over values of 128 on the tcgen05 kernel (out's columns from v_dim on become zeros)
+                self._call("zlm_attention_prefill_tc_vd", self._p(out), c_int(out.stride(0)),
+                           self._p(q), c_int(q.stride(0)), c_int(T), self._p(pool),
+                           ctypes.c_longlong(pool.shape[0]), self._p(block_table),
+                           c_int(block_table.stride(0)), self._p(plan.cu_seqlens),
+                           self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R),
+                           c_int(plan.max_new), c_int(nq), c_int(nkv), c_int(hd), c_int(v_dim), c_float(scale),
+                           c_int(window), sk, *extra, self._stream())
+                return
             if v_dim is not None and v_dim < hd and self.lib.zlm_attention_prefill_vd_supported(nq, nkv, hd, v_dim):
                 # values narrower than keys (their rows in the pool are padded to the keys' width): the padding is
                 # neither loaded nor multiplied, and out's columns from v_dim on become zeros
