@@ -558,12 +558,12 @@ def _lodevik(width, heads, kv_heads, chunk, ff, kinds, vocab):
     half = width <= 1024
     lat = {"heads": heads, "dim": 64 if half else 128, "rot_dim": 32 if half else 64, "vdim": 64 if half else 128,
            "kv_rank": 256 if half else 512, "scale": (96 if half else 192) ** -0.5,
-           "rot": {"base": 250000.0, "dims": 32 if half else 64}}
+           "rot": {"base": 100000.0, "dims": 32 if half else 64}}
     att = {"heads": heads, "kv_heads": kv_heads, "dim": 32 if half else 64, "vdim": 64 if half else 128,
-           "scale": (32 if half else 64) ** -0.5, "softcap": 50.0, "diff": 0.3, "mask": {"size": chunk},
-           "rot": {"base": 50000.0, "dims": 16 if half else 32}}
+           "scale": (32 if half else 64) ** -0.5, "softcap": 30.0, "diff": 0.2, "mask": {"size": chunk},
+           "rot": {"base": 10000.0, "dims": 16 if half else 32}}
     return {"architecture": "Lodevik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 1.0,
-            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}},
             "layers": [{"type": "attention" if k == "a" else "latent_attention", "mixer": dict(att if k == "a" else lat),
                         "mlp": {"kind": "dense", "ff": ff}} for k in kinds]}
 

@@ -59,8 +59,8 @@ LODE_B = {
     "architecture": "Lodevik", "vocab": 200, "width": 128, "norm": {"eps": 1e-6},
     "embedding": {"scale": 1.0},
     "layers": [
-        _layer("latent_attention", _lat(5, 32, 32, 48, 64, 0.15, 250000.0, 32), 96),
-        _layer("attention", _att(6, 1, 32, 64, 0.18, 0.3, 50.0, 50000.0, 16, 64), 64),
+        _layer("latent_attention", _lat(5, 32, 32, 48, 64, 0.15, 100000.0, 32), 96),
+        _layer("attention", _att(6, 1, 32, 64, 0.18, 0.35, 40.0, 20000.0, 16, 64), 64),
         _layer("latent_attention", _lat(2, 48, 16, 32, 24, 0.12, 1000.0, 16, 128), 0),
         _layer("attention", _att(2, 2, 56, 24, 0.13, 0.6, 1.5, 10.0, 56), 72),
     ],
