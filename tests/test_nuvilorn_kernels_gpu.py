@@ -114,8 +114,9 @@ def test_prep_norms_rotates_and_writes_records(dtype, H, dn, dr, r, n_rot):
     inv = (base ** (-2.0 * i / max(n_rot, 1))).float().cuda() if n_rot else None
     dev = qd.cuda()
     qrot = torch.zeros(T, H, dr, dtype=DT[dtype], device="cuda")
+    rows = torch.zeros(T, R, dtype=DT[dtype], device="cuda")
     k.latent_prep(dev[:, :H * Dq], qrot, dev[:, H * Dq:], cw.cuda(), eps, inv, n_rot, positions.cuda(),
-                  torch.zeros(T, dtype=torch.int32, device="cuda"), table.cuda(), pool, H, dn, dr, r)
+                  torch.zeros(T, dtype=torch.int32, device="cuda"), table.cuda(), pool, H, dn, dr, r, rec_out=rows)
     x = qd.double()
     c = P.vector_norm(x[:, H * Dq:H * Dq + r], cw.double(), eps)
     kr = P.rotate_pairs(x[:, H * Dq + r:], positions, base, n_rot)
@@ -123,6 +124,7 @@ def test_prep_norms_rotates_and_writes_records(dtype, H, dn, dr, r, n_rot):
     close(qrot, qr, dtype, "rotated query parts")
     got = torch.stack([pool[table[0, p // PAGE], p % PAGE] for p in positions.tolist()])
     close(got, torch.cat([c, kr], dim=1), dtype, "records")
+    assert torch.equal(rows, got), "the records' plain rows differ from the pages"
     # in place, and without a record (a layer that reads another layer's latents)
     q3 = dev[:, :H * Dq].view(T, H, Dq)
     before = dev.clone()

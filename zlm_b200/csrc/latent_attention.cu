@@ -19,14 +19,15 @@
 
 // ---------------------------------------------------------------------------- prep
 // One block per token.  q [T, H, dn + dr] and dkv [T, r + dr] are views of the fused projection's rows
-// (dkv is absent for a layer that reads another layer's records).
+// (dkv is absent for a layer that reads another layer's records).  rec_out (may be null): the token's record also goes
+// to row t of a plain matrix [T, r + dr], for a step that multiplies its own records at once.
 template <typename TA>
 __global__ void __launch_bounds__(128)
 latent_prep_kernel(const TA* q, int q_stride, TA* qo, int qo_stride, int qo_hstride,
                    const TA* __restrict__ dkv, int dkv_stride, VecW cw, float eps,
                    const float* __restrict__ inv_freq, int n_rot, const int* __restrict__ token_pos,
                    const int* __restrict__ token_slot, const int* __restrict__ block_table, int table_stride,
-                   TA* __restrict__ pool, int H, int dn, int dr, int r) {
+                   TA* __restrict__ pool, int H, int dn, int dr, int r, TA* __restrict__ rec_out, int rec_stride) {
     __shared__ float red[32];
     __shared__ float cs[2][256];               // cos, sin of the token's angles
     pdl_trigger();
@@ -69,6 +70,8 @@ latent_prep_kernel(const TA* q, int q_stride, TA* qo, int qo_stride, int qo_hstr
     const TA* src = dkv + (size_t)t * dkv_stride;
     TA* rec = pool + ((size_t)page * ZLM_PAGE + pos % ZLM_PAGE) * (r + dr);
     if (!ZLM_CHK(src, (size_t)(r + dr) * sizeof(TA)) || !ZLM_CHK(rec, (size_t)(r + dr) * sizeof(TA))) return;
+    TA* row = rec_out ? rec_out + (size_t)t * rec_stride : nullptr;
+    if (row && !ZLM_CHK(row, (size_t)(r + dr) * sizeof(TA))) return;
     float ss = 0.f;
     for (int i = threadIdx.x; i < r; i += blockDim.x) {
         const float a = to_f32(src[i]);
@@ -76,21 +79,32 @@ latent_prep_kernel(const TA* q, int q_stride, TA* qo, int qo_stride, int qo_hstr
     }
     ss = block_sum(ss, red);
     const float inv = 1.0f / sqrtf(ss / (float)r + eps);
-    for (int i = threadIdx.x; i < r; i += blockDim.x) rec[i] = from_f32<TA>((to_f32(src[i]) * inv) * cw[i]);
+    for (int i = threadIdx.x; i < r; i += blockDim.x) {
+        const TA c = from_f32<TA>((to_f32(src[i]) * inv) * cw[i]);
+        rec[i] = c;
+        if (row) row[i] = c;
+    }
     for (int i = threadIdx.x; i < ang; i += blockDim.x) {
         const float u = to_f32(src[r + 2 * i]), v = to_f32(src[r + 2 * i + 1]);
-        rec[r + 2 * i] = from_f32<TA>(u * cs[0][i] - v * cs[1][i]);
-        rec[r + 2 * i + 1] = from_f32<TA>(v * cs[0][i] + u * cs[1][i]);
+        const TA a = from_f32<TA>(u * cs[0][i] - v * cs[1][i]), b = from_f32<TA>(v * cs[0][i] + u * cs[1][i]);
+        rec[r + 2 * i] = a;
+        rec[r + 2 * i + 1] = b;
+        if (row) { row[r + 2 * i] = a; row[r + 2 * i + 1] = b; }
     }
-    for (int i = n_rot + threadIdx.x; i < dr; i += blockDim.x) rec[r + i] = src[r + i];
+    for (int i = n_rot + threadIdx.x; i < dr; i += blockDim.x) {
+        rec[r + i] = src[r + i];
+        if (row) row[r + i] = src[r + i];
+    }
 }
 
 extern "C" int zlm_latent_prep(const void* q, int q_stride, void* qo, int qo_stride, int qo_hstride, const void* dkv,
                                int dkv_stride, int dtype, const void* cw,
                                int cw_dtype, float eps, const float* inv_freq, int n_rot, const int* token_pos,
                                const int* token_slot, const int* block_table, int table_stride, void* pool, int T,
-                               int H, int dn, int dr, int r, cudaStream_t st) {
+                               int H, int dn, int dr, int r, void* rec_out, int rec_stride, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(rec_out == nullptr || (dkv != nullptr && rec_stride >= r + dr), "latent_prep: the records' second place needs "
+                "the projection and rows of at least %d elements", r + dr);
     ZLM_REQUIRE(H > 0 && dn >= 0 && dr >= 0 && r > 0, "latent_prep: bad sizes heads=%d dim=%d rot_dim=%d kv_rank=%d", H, dn, dr, r);
     ZLM_REQUIRE(n_rot >= 0 && n_rot % 2 == 0 && n_rot <= dr && n_rot <= 512,
                 "latent_prep: %d rotated dimensions of %d (even, at most 512)", n_rot, dr);
@@ -100,11 +114,12 @@ extern "C" int zlm_latent_prep(const void* q, int q_stride, void* qo, int qo_str
     if (dtype == ZLM_DTYPE_F32)
         zlm_launch(latent_prep_kernel<float>, T, 128, 0, st, (const float*)q, q_stride, (float*)qo, qo_stride, qo_hstride,
                    (const float*)dkv, dkv_stride, w, eps,
-                   inv_freq, n_rot, token_pos, token_slot, block_table, table_stride, (float*)pool, H, dn, dr, r);
+                   inv_freq, n_rot, token_pos, token_slot, block_table, table_stride, (float*)pool, H, dn, dr, r,
+                   (float*)rec_out, rec_stride);
     else if (dtype == ZLM_DTYPE_BF16)
         zlm_launch(latent_prep_kernel<__nv_bfloat16>, T, 128, 0, st, (const __nv_bfloat16*)q, q_stride,
                    (__nv_bfloat16*)qo, qo_stride, qo_hstride, (const __nv_bfloat16*)dkv, dkv_stride, w, eps, inv_freq, n_rot, token_pos, token_slot, block_table,
-                   table_stride, (__nv_bfloat16*)pool, H, dn, dr, r);
+                   table_stride, (__nv_bfloat16*)pool, H, dn, dr, r, (__nv_bfloat16*)rec_out, rec_stride);
     else
         ZLM_REQUIRE(false, "latent_prep: unsupported dtype %d", dtype);
     return zlm_check_launch("latent_prep");

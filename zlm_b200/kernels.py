@@ -799,15 +799,17 @@ class CudaKernels:
                     c_weight: Optional[torch.Tensor], eps: float,
                     inv_freq: Optional[torch.Tensor], n_rot: int, token_pos: torch.Tensor, token_slot: torch.Tensor,
                     block_table: Optional[torch.Tensor], pool: Optional[torch.Tensor], heads: int, dim: int,
-                    rot_dim: int, kv_rank: int) -> None:
+                    rot_dim: int, kv_rank: int, rec_out: Optional[torch.Tensor] = None) -> None:
         """Per token: the rotated parts of the heads' queries (q [T, heads * (dim + rot_dim)], each head
         [dim | rot_dim]) are turned by the token's position, neighbouring pairs (2i, 2i+1) by
         pos * inv_freq[i], and written to q_rot [T, heads, rot_dim] (any token and head strides; it may
         be the view q[:, :, dim:] itself); and, where ``dkv`` [T, kv_rank + rot_dim] is given, the token's record
         [RMSNorm(dkv[:kv_rank]) * c_weight | rotated dkv[kv_rank:]] goes to its place in the paged
-        ``pool`` [pages, PAGE_TOKENS, kv_rank + rot_dim]."""
+        ``pool`` [pages, PAGE_TOKENS, kv_rank + rot_dim], and also to row t of ``rec_out`` [T, kv_rank + rot_dim] if given."""
         T = q.shape[0]
         assert q.shape[1] == heads * (dim + rot_dim) and q.stride(1) == 1
+        assert rec_out is None or (dkv is not None and rec_out.shape == (T, kv_rank + rot_dim) and rec_out.stride(1) == 1
+                                   and rec_out.dtype == q.dtype)
         assert q_rot.shape == (T, heads, rot_dim) and q_rot.dtype == q.dtype and (rot_dim == 0 or q_rot.stride(2) == 1)
         if inv_freq is not None:
             assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot
@@ -824,7 +826,8 @@ class CudaKernels:
                    c_int(_dt(c_weight) if dkv is not None else F32), c_float(eps), self._p(inv_freq), c_int(n_rot),
                    self._p(token_pos), self._p(token_slot), self._p(block_table if dkv is not None else None),
                    c_int(block_table.stride(0) if dkv is not None else 0), self._p(pool if dkv is not None else None),
-                   c_int(T), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank), self._stream())
+                   c_int(T), c_int(heads), c_int(dim), c_int(rot_dim), c_int(kv_rank), self._p(rec_out),
+                   c_int(rec_out.stride(0) if rec_out is not None else 0), self._stream())
 
     def latent_gather(self, rec: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, token_pos: torch.Tensor,
                       token_slot: torch.Tensor) -> None:

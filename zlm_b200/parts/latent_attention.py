@@ -231,12 +231,18 @@ class LatentAttention(Mixer):
         k.linear(qd, x, self.w_in)
         q = qd[:, : self.Q]
         q3 = qd.as_strided((T, H, self.Dq), (qd.stride(0), self.Dq, 1))
-        # rotated query parts in place; the records into their pages
-        k.latent_prep(q, q3[:, :, dn:], qd[:, self.Q: self.Q + R] if writes else None, self.c_norm, self.eps,
-                      self.position.inv_freq, self.position.n_rot, ctx.token_pos, ctx.token_slot,
-                      cache.block_table, cache.pool, H, dn, dr, r)
+        # rotated query parts in place; the records into their pages and, for this step's products, into plain rows
+        # (a layer that reads another layer's records gathers them from the pages instead)
         rec = rt.ws.get("lat.rec", (T, R), rt.dtype)
-        k.latent_gather(rec, cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot)
+        if writes:
+            k.latent_prep(q, q3[:, :, dn:], qd[:, self.Q: self.Q + R], self.c_norm, self.eps,
+                          self.position.inv_freq, self.position.n_rot, ctx.token_pos, ctx.token_slot,
+                          cache.block_table, cache.pool, H, dn, dr, r, rec_out=rec)
+        else:
+            k.latent_prep(q, q3[:, :, dn:], None, self.c_norm, self.eps,
+                          self.position.inv_freq, self.position.n_rot, ctx.token_pos, ctx.token_slot,
+                          cache.block_table, cache.pool, H, dn, dr, r)
+            k.latent_gather(rec, cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot)
         kv = rt.ws.get("lat.kv", (T, H * (dn + dv)), rt.dtype)
         k.linear(kv, rec[:, :r], self.w_ukv)
         table, rows, pages = self._step_pages(ctx)
