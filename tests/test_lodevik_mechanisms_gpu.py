@@ -510,3 +510,34 @@ def test_one_gate_number_per_head(K, dtype, H, V):
     want = x.double().cpu() * torch.sigmoid(g.double().cpu())[:, :, None]
     K.head_scalar_gate(x, g)
     close(x.reshape(T, H * V), want.reshape(T, H * V), dtype, tol=1e-6 if dtype == "float32" else 6e-3)
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# per-head keys and values of a step written out for the flash kernels
+# ---------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H, dn, dr, dv, r", [(3, 32, 32, 48, 64), (2, 128, 64, 128, 96), (5, 12, 4, 10, 20), (1, 8, 8, 16, 8),
+                                              (4, 48, 16, 20, 40)])
+def test_keys_and_values_of_a_step_are_written_out(K, dtype, H, dn, dr, dv, r):
+    """Two sequences of 70 and 5 tokens: K = [the head's unrotated key | the record's rotated part], V = [the head's
+    value | zeros], at the token's place of its sequence's own pages; sizes that are multiples of 8 (pieces of 16
+    bytes in bfloat16) and sizes that are not; a buffer that held other numbers before."""
+    dt = DT[dtype]
+    hd, lens = dn + dr, [70, 5]
+    T = sum(lens)
+    kv = rnd((T, H * (dn + dv)), 3).to(dt)
+    rec = rnd((T, r + dr), 4).to(dt)
+    pos = torch.tensor([p for n in lens for p in range(n)], dtype=torch.int32)
+    seq = torch.tensor([i for i, n in enumerate(lens) for _ in range(n)], dtype=torch.int32)
+    table = torch.tensor([[2, 0], [1, 0]], dtype=torch.int32)
+    spool = torch.full((3, 2, H, PAGE, hd), 7.0, dtype=dt, device="cuda")
+    K.latent_unfold(spool, table.cuda(), kv.cuda(), rec.cuda(), pos.cuda(), seq.cuda(), H, dn, dr, dv, r)
+    got = spool.cpu()
+    for t in range(T):
+        page, place = int(table[seq[t], pos[t] // PAGE]), int(pos[t]) % PAGE
+        for h in range(H):
+            want_k = torch.cat([kv[t, h * dn:(h + 1) * dn], rec[t, r:]])
+            want_v = torch.cat([kv[t, H * dn + h * dv: H * dn + (h + 1) * dv], torch.zeros(hd - dv, dtype=dt)])
+            assert torch.equal(got[page, 0, h, place], want_k) and torch.equal(got[page, 1, h, place], want_v), (t, h)
+    # places that no token has keep what they held
+    assert bool((got[0, :, :, 6:] == 7.0).all()) and bool((got[1, :, :, 5:] == 7.0).all())

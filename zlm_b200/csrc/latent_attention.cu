@@ -416,6 +416,38 @@ latent_unfold_kernel(TA* __restrict__ spool, const int* __restrict__ stable, int
     }
 }
 
+// the same in pieces of 8 elements (16 bytes), for bfloat16 with every width a multiple of 8: a thread copies a piece
+// of a head's key and the piece of its value at the same columns
+__global__ void __launch_bounds__(256)
+latent_unfold_v8_kernel(__nv_bfloat16* __restrict__ spool, const int* __restrict__ stable, int stable_stride,
+                        const __nv_bfloat16* __restrict__ kv, int kv_stride, const __nv_bfloat16* __restrict__ rec,
+                        int rec_stride, const int* __restrict__ token_pos, const int* __restrict__ token_seq, int H, int dn,
+                        int dr, int dv, int r) {
+    pdl_launch_dependents();
+    const int t = blockIdx.x, hd = dn + dr, per = hd / 8;
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_seq + t, 4)) return;
+    const int pos = token_pos[t], seq = token_seq[t];
+    if (!ZLM_CHK(stable + (size_t)seq * stable_stride + pos / ZLM_PAGE, 4)) return;
+    const int page = stable[(size_t)seq * stable_stride + pos / ZLM_PAGE];
+    pdl_wait();
+    const size_t tile = (size_t)ZLM_PAGE * hd;
+    __nv_bfloat16* kbase = spool + (size_t)page * 2 * H * tile + (size_t)(pos % ZLM_PAGE) * hd;
+    __nv_bfloat16* vbase = kbase + (size_t)H * tile;
+    const __nv_bfloat16* kvr = kv + (size_t)t * kv_stride;
+    const __nv_bfloat16* kr = rec + (size_t)t * rec_stride + r;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (int c = threadIdx.x; c < H * per; c += blockDim.x) {
+        const int h = c / per, i = (c - h * per) * 8;
+        __nv_bfloat16* kd = kbase + (size_t)h * tile + i;
+        __nv_bfloat16* vd = vbase + (size_t)h * tile + i;
+        if (!ZLM_CHK(kd, 16) || !ZLM_CHK(vd, 16)) continue;
+        const __nv_bfloat16* ks = i < dn ? kvr + (size_t)h * dn + i : kr + (i - dn);
+        *(uint4*)kd = ZLM_CHK(ks, 16) ? *(const uint4*)ks : zero;
+        const __nv_bfloat16* vs = kvr + (size_t)H * dn + (size_t)h * dv + i;
+        *(uint4*)vd = (i < dv && ZLM_CHK(vs, 16)) ? *(const uint4*)vs : zero;
+    }
+}
+
 extern "C" int zlm_latent_gather(void* rec, const void* pool, const int* block_table, int table_stride,
                                  const int* token_pos, const int* token_slot, int dtype, int T, int R, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
@@ -440,6 +472,11 @@ extern "C" int zlm_latent_unfold(void* spool, const int* stable, int stable_stri
     if (dtype == ZLM_DTYPE_F32)
         zlm_launch(latent_unfold_kernel<float>, T, 256, 0, st, (float*)spool, stable, stable_stride, (const float*)kv, kv_stride,
                    (const float*)rec, rec_stride, token_pos, token_seq, H, dn, dr, dv, r);
+    else if (dtype == ZLM_DTYPE_BF16 && dn % 8 == 0 && dr % 8 == 0 && dv % 8 == 0 && r % 8 == 0 && kv_stride % 8 == 0 &&
+             rec_stride % 8 == 0 && (uintptr_t)spool % 16 == 0 && (uintptr_t)kv % 16 == 0 && (uintptr_t)rec % 16 == 0)
+        zlm_launch(latent_unfold_v8_kernel, T, 256, 0, st, (__nv_bfloat16*)spool, stable, stable_stride,
+                   (const __nv_bfloat16*)kv, kv_stride, (const __nv_bfloat16*)rec, rec_stride, token_pos, token_seq, H, dn, dr,
+                   dv, r);
     else if (dtype == ZLM_DTYPE_BF16)
         zlm_launch(latent_unfold_kernel<__nv_bfloat16>, T, 256, 0, st, (__nv_bfloat16*)spool, stable, stable_stride,
                    (const __nv_bfloat16*)kv, kv_stride, (const __nv_bfloat16*)rec, rec_stride, token_pos, token_seq, H, dn, dr,
