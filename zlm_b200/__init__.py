@@ -4,9 +4,9 @@ layers put together from parts, a paged cache with slots, one step function, a
 generation loop, samplers, and the CUDA kernels under them."""
 from . import models as _models          # fills the architecture registry
 from . import parts as _parts            # fills the part registries
-from .config import ConfigError, LodevikConfig, NuvilornConfig, Qwen3Config, ZekazenConfig
+from .config import ConfigError, LodevikConfig, NuvilornConfig, Qwen3Config, SudupelConfig, ZekazenConfig
 from .engine import Engine, StepEntry, StepError
 from .weights import WeightError, write_random_model
 
-__all__ = ["ConfigError", "LodevikConfig", "NuvilornConfig", "Qwen3Config", "ZekazenConfig", "Engine", "StepEntry", "StepError", "WeightError",
+__all__ = ["ConfigError", "LodevikConfig", "NuvilornConfig", "Qwen3Config", "SudupelConfig", "ZekazenConfig", "Engine", "StepEntry", "StepError", "WeightError",
            "write_random_model"]

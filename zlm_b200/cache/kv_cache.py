@@ -203,7 +203,16 @@ class KVCache:
                     raise ValueError(f"schedule[{i}] cannot read the cache of entry {src}: different head layout")
                 view = CacheView(pool=g.pool[j], block_table=g.block_table, writes=e.cache_of is None, group=g)
             st = None
-            if s is not None:
+            if isinstance(s, (tuple, list)):
+                # a mixer made of several (mixers side by side): one tensor per request, None where one asked for nothing
+                made = []
+                for one in s:
+                    made.append(None if one is None else
+                                torch.zeros((self.max_slots, *one.shape), dtype=one.dtype, device=device))
+                    if made[-1] is not None:
+                        self.state_tensors.append(made[-1])
+                st = tuple(made)
+            elif s is not None:
                 st = torch.zeros((self.max_slots, *s.shape), dtype=s.dtype, device=device)
                 self.state_tensors.append(st)
             self.ios.append(LayerIO(cache=view, state=st))

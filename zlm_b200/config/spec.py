@@ -42,12 +42,16 @@ class PartSpec:
 class LayerSpec:
     """A block: how a mixer and a feed-forward are arranged around the residual
     stream, and the norms that go with them.  ``arrangement`` names a registered
-    block class (``pre_norm``: h += mixer(norm(h)); h += ffn(norm(h)))."""
+    block class (``pre_norm``: h += mixer(norm(h)); h += ffn(norm(h))).  An arrangement with a norm on each
+    sublayer's output as well as on its input (``sandwich_norm``) names those in ``mixer_post_norm`` and
+    ``feed_forward_post_norm``."""
     arrangement: str
     mixer: PartSpec
     feed_forward: PartSpec
     mixer_norm: PartSpec
     feed_forward_norm: PartSpec
+    mixer_post_norm: Optional[PartSpec] = None
+    feed_forward_post_norm: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)

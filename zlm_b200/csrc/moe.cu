@@ -72,7 +72,7 @@ __device__ __forceinline__ void warp_argmax(const float* v, int n, int lane, flo
 
 __device__ __forceinline__ void route_choose(float* sc, float* cs, float* gm, int* __restrict__ idx, float* __restrict__ wgt,
                                              int t, int lane, int E, int top, int score_kind, int renorm,
-                                             const float* __restrict__ corr, int groups, int keep, float wscale) {
+                                             const float* __restrict__ corr, int groups, int keep, int group_top, float wscale) {
     if (score_kind == 1) {
         float mx = -INFINITY;
         for (int e = lane; e < E; e += 32) mx = fmaxf(mx, sc[e]);
@@ -91,9 +91,12 @@ __device__ __forceinline__ void route_choose(float* sc, float* cs, float* gm, in
     if (groups > 1 && keep < groups) {
         const int size = E / groups;
         for (int g = lane; g < groups; g += 32) {
-            float m = -INFINITY;
-            for (int e = g * size; e < (g + 1) * size; ++e) m = fmaxf(m, cs[e]);
-            gm[g] = m;
+            float m = -INFINITY, m2 = -INFINITY;                    // the group's largest and second largest choice score
+            for (int e = g * size; e < (g + 1) * size; ++e) {
+                const float x = cs[e];
+                if (x > m) { m2 = m; m = x; } else if (x > m2) { m2 = x; }
+            }
+            gm[g] = (group_top >= 2 && size >= 2) ? m + m2 : m;
         }
         __syncwarp();
         for (int j = 0; j < keep; ++j) {
@@ -135,7 +138,7 @@ template <typename TA, int TOK>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 moe_route_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restrict__ gate, const TA* __restrict__ x,
                  int x_stride, const TA* __restrict__ Wr, const TA* __restrict__ wg, int T, int E, int K, int top,
-                 int score_kind, int renorm, const float* __restrict__ corr, int groups, int keep, float wscale) {
+                 int score_kind, int renorm, const float* __restrict__ corr, int groups, int keep, int group_top, float wscale) {
     extern __shared__ float sc_all[];           // [TOK][2E + groups]: scores, choice scores, the groups' best
     pdl_trigger();
     const int t0 = blockIdx.x * TOK, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -183,7 +186,7 @@ moe_route_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restri
     __syncthreads();
     if (warp >= TOK || t0 + warp >= T) return;
     float* sc = sc_all + warp * (2 * E + groups);
-    route_choose(sc, sc + E, sc + 2 * E, idx, wgt, t0 + warp, lane, E, top, score_kind, renorm, corr, groups, keep, wscale);
+    route_choose(sc, sc + E, sc + 2 * E, idx, wgt, t0 + warp, lane, E, top, score_kind, renorm, corr, groups, keep, group_top, wscale);
 }
 
 // The same choice from logits that a product of the library left in fp32 (bf16 steps: the router's matrix, with the
@@ -192,7 +195,7 @@ moe_route_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restri
 __global__ void __launch_bounds__(128)
 moe_choose_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restrict__ gate, const float* __restrict__ logits,
                   int ld, int T, int E, int top, int has_gate, int score_kind, int renorm, const float* __restrict__ corr,
-                  int groups, int keep, float wscale) {
+                  int groups, int keep, int group_top, float wscale) {
     extern __shared__ float sc_all[];           // [4][2E + groups]
     pdl_trigger();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -205,7 +208,7 @@ moe_choose_kernel(int* __restrict__ idx, float* __restrict__ wgt, float* __restr
         if (ZLM_CHK(z + e, 4)) sc[e] = score_kind == 0 ? 1.0f / (1.0f + expf(-z[e])) : z[e];
     if (has_gate && lane == 0 && ZLM_CHK(z + E, 4) && ZLM_CHK(gate + t, 4)) gate[t] = 1.0f / (1.0f + expf(-z[E]));
     __syncwarp();
-    route_choose(sc, sc + E, sc + 2 * E, idx, wgt, t, lane, E, top, score_kind, renorm, corr, groups, keep, wscale);
+    route_choose(sc, sc + E, sc + 2 * E, idx, wgt, t, lane, E, top, score_kind, renorm, corr, groups, keep, group_top, wscale);
 }
 
 static int route_groups_ok(int E, int top, int groups, int keep) {
@@ -218,44 +221,44 @@ static int route_groups_ok(int E, int top, int groups, int keep) {
 // groups of neighbours and only the `keep` best groups (by their largest choice score) can be chosen; wscale multiplies
 // the weights.  1, 1, 1.0 and no corr give the plain top-k.
 extern "C" int zlm_moe_choose(int* idx, float* wgt, float* gate, const float* logits, int ld, int T, int E, int top,
-                              int has_gate, int score_kind, int renorm, const float* corr, int groups, int keep,
+                              int has_gate, int score_kind, int renorm, const float* corr, int groups, int keep, int group_top,
                               float wscale, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
     if (int rc = route_groups_ok(E, top, groups, keep)) return rc;
     ZLM_REQUIRE(E > 0 && E <= 2048 && top > 0 && top <= E && ld >= E + (has_gate ? 1 : 0), "moe_choose: experts=%d top=%d ld=%d", E, top, ld);
     ZLM_REQUIRE(!has_gate || gate, "moe_choose: a shared gate needs a place for its values");
     zlm_launch(moe_choose_kernel, (T + 3) / 4, 128, (size_t)4 * (2 * E + groups) * sizeof(float), st, idx, wgt, gate, logits, ld,
-               T, E, top, has_gate, score_kind, renorm, corr, groups, keep, wscale);
+               T, E, top, has_gate, score_kind, renorm, corr, groups, keep, group_top, wscale);
     return zlm_check_launch("moe_choose");
 }
 
 template <typename TA>
 static void launch_route(int* idx, float* wgt, float* gate, const void* x, int x_stride, const void* Wr, const void* wg,
-                         int T, int E, int K, int top, int score_kind, int renorm, const float* corr, int groups, int keep,
+                         int T, int E, int K, int top, int score_kind, int renorm, const float* corr, int groups, int keep, int group_top,
                          float wscale, cudaStream_t st) {
     // many tokens: four a block (a quarter of the reads of the router's matrix); few: one, so that the blocks are many
     if (T >= 64)
         zlm_launch(moe_route_kernel<TA, 4>, (T + 3) / 4, ROUTE_WARPS * 32, (size_t)4 * (2 * E + groups) * sizeof(float), st, idx,
                    wgt, gate, (const TA*)x, x_stride, (const TA*)Wr, (const TA*)wg, T, E, K, top, score_kind, renorm, corr, groups,
-                   keep, wscale);
+                   keep, group_top, wscale);
     else
         zlm_launch(moe_route_kernel<TA, 1>, T, ROUTE_WARPS * 32, (size_t)(2 * E + groups) * sizeof(float), st, idx, wgt, gate,
-                   (const TA*)x, x_stride, (const TA*)Wr, (const TA*)wg, T, E, K, top, score_kind, renorm, corr, groups, keep,
+                   (const TA*)x, x_stride, (const TA*)Wr, (const TA*)wg, T, E, K, top, score_kind, renorm, corr, groups, keep, group_top,
                    wscale);
 }
 
 extern "C" int zlm_moe_route(int* idx, float* wgt, float* gate, const void* x, int x_stride, const void* Wr,
                              const void* wg, int dtype, int T, int E, int K, int top, int score_kind, int renorm,
-                             const float* corr, int groups, int keep, float wscale, cudaStream_t st) {
+                             const float* corr, int groups, int keep, int group_top, float wscale, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
     if (int rc = route_groups_ok(E, top, groups, keep)) return rc;
     ZLM_REQUIRE(E > 0 && E <= 2048 && K > 0 && top > 0 && top <= E, "moe_route: experts=%d top=%d K=%d", E, top, K);
     ZLM_REQUIRE(score_kind == 0 || score_kind == 1, "moe_route: score kind %d", score_kind);
     ZLM_REQUIRE(wg == nullptr || gate != nullptr, "moe_route: a shared gate needs a place for its values");
     if (dtype == ZLM_DTYPE_F32)
-        launch_route<float>(idx, wgt, gate, x, x_stride, Wr, wg, T, E, K, top, score_kind, renorm, corr, groups, keep, wscale, st);
+        launch_route<float>(idx, wgt, gate, x, x_stride, Wr, wg, T, E, K, top, score_kind, renorm, corr, groups, keep, group_top, wscale, st);
     else if (dtype == ZLM_DTYPE_BF16)
-        launch_route<__nv_bfloat16>(idx, wgt, gate, x, x_stride, Wr, wg, T, E, K, top, score_kind, renorm, corr, groups, keep,
+        launch_route<__nv_bfloat16>(idx, wgt, gate, x, x_stride, Wr, wg, T, E, K, top, score_kind, renorm, corr, groups, keep, group_top,
                                     wscale, st);
     else
         ZLM_REQUIRE(false, "moe_route: unsupported dtype %d", dtype);

@@ -278,4 +278,246 @@ extern "C" int zlm_head_gate(void* out, int out_stride, const void* o, int o_is_
     return zlm_check_launch("head_gate");
 }
 
+
+// ---------------------------------------------------------------------------- q/k/v preparation, general form
+// What stands between a fused q/k/v projection and attention over the paged cache, with every step optional:
+//   a short causal convolution per channel (as above; has_conv 0: none),
+//   a norm of q and k: per head without weight (norm_mode 1), per head with one weight of `dim` shared by the heads
+//   (2), or over the whole projection at once, all heads of q (of k) together, with a weight per channel (3),
+//   rotation of the first n_rot coordinates of every q and k head, coordinate i against i + n_rot/2, by the angle
+//   pos * inv_freq[i]; cosine and sine are multiplied by rot_scale (a frequency table scaled for long contexts
+//   carries such a factor),
+//   q written head by head, k and v into the token's place of the paged cache, heads padded with zeros to hdp.
+// A block per token: the token's convolved channels are held in shared memory as fp32, the sums of squares are
+// block sums in a fixed order, angles, cosines and sines are fp32.
+#define AP_THREADS 256
+template <typename TA>
+__global__ void __launch_bounds__(AP_THREADS)
+attn_prep_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __restrict__ proj, int proj_stride,
+                 const TA* __restrict__ conv_w, const TA* __restrict__ state, const int* __restrict__ token_pos,
+                 const int* __restrict__ token_slot, const int* __restrict__ token_seq, const int* __restrict__ seq_start,
+                 const int* __restrict__ cu_seqlens, const int* __restrict__ block_table, int table_stride,
+                 TA* __restrict__ pool, int nq, int nkv, int dim, int vdim, int hdp, int taps, int norm_mode, VecW q_w,
+                 VecW k_w, float eps, const float* __restrict__ inv_freq, int n_rot, float rot_scale) {
+    extern __shared__ float ap_smem[];          // [C] channels, [nq + nkv] inverse root mean squares, [32] reduction
+    pdl_trigger();
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int QC = nq * dim, KC = nkv * dim, C = QC + KC + nkv * vdim;
+    float* val = ap_smem;
+    float* inv = ap_smem + C;
+    float* red = inv + nq + nkv;
+    pdl_wait();
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4) || !ZLM_CHK(token_seq + t, 4)) return;
+    const int pos = token_pos[t], slot = token_slot[t], r = token_seq[t];
+    if (!ZLM_CHK(seq_start + r, 4) || !ZLM_CHK(cu_seqlens + r, 4)) return;
+    const int i = pos - seq_start[r];
+    const int row0 = cu_seqlens[r];
+    float ssq = 0.f, ssk = 0.f;
+    for (int c = tid; c < C; c += AP_THREADS) {
+        float a = 0.f;
+        if (conv_w) {
+            for (int j = 0; j < taps; ++j) {
+                const int s = i - (taps - 1) + j;
+                if (pos - (taps - 1) + j < 0) continue;
+                const TA* up = s >= 0 ? proj + (size_t)(row0 + s) * proj_stride + c
+                                      : state + ((size_t)slot * (taps - 1) + (taps - 1 + s)) * C + c;
+                if (!ZLM_CHK(up, sizeof(TA)) || !ZLM_CHK(conv_w + (size_t)c * taps + j, sizeof(TA))) continue;
+                a = fmaf(to_f32(conv_w[(size_t)c * taps + j]), to_f32(*up), a);
+            }
+        } else {
+            const TA* up = proj + (size_t)(row0 + i) * proj_stride + c;
+            if (ZLM_CHK(up, sizeof(TA))) a = to_f32(*up);
+        }
+        val[c] = a;
+        if (c < QC) ssq = fmaf(a, a, ssq); else if (c < QC + KC) ssk = fmaf(a, a, ssk);
+    }
+    __syncthreads();
+    if (norm_mode == 3) {
+        const float tq = block_sum(ssq, red);
+        const float tk = block_sum(ssk, red);
+        if (tid == 0) {
+            const float iq = 1.0f / sqrtf(tq / (float)QC + eps), ik = 1.0f / sqrtf(tk / (float)KC + eps);
+            for (int h = 0; h < nq; ++h) inv[h] = iq;
+            for (int h = 0; h < nkv; ++h) inv[nq + h] = ik;
+        }
+    } else {
+        for (int h = warp; h < nq + nkv; h += AP_THREADS / 32) {
+            float ss = 0.f;
+            for (int e = lane; e < dim; e += 32) { const float a = val[h * dim + e]; ss = fmaf(a, a, ss); }
+            ss = warp_sum(ss);
+            if (lane == 0) inv[h] = norm_mode ? 1.0f / sqrtf(ss / (float)dim + eps) : 1.0f;
+        }
+    }
+    __syncthreads();
+    // q and k heads: norm, weight, rotation, write
+    const int half = n_rot / 2;
+    int page = 0;
+    if (ZLM_CHK(block_table + (size_t)slot * table_stride + pos / ZLM_PAGE, 4))
+        page = block_table[(size_t)slot * table_stride + pos / ZLM_PAGE];
+    for (int x = tid; x < (nq + 2 * nkv) * hdp; x += AP_THREADS) {
+        const int unit = x / hdp, e = x - unit * hdp;
+        float o = 0.f;
+        if (unit < nq + nkv) {
+            if (e < dim) {
+                const int c = unit * dim + e;
+                const VecW& w = unit < nq ? q_w : k_w;
+                const int wb = norm_mode == 3 ? (unit < nq ? unit * dim : (unit - nq) * dim) : 0;
+                const float sc = inv[unit];
+                o = val[c] * sc * (norm_mode >= 2 ? w[wb + e] : 1.0f);
+                if (e < n_rot) {
+                    const int fi = e < half ? e : e - half;
+                    const int pe = e < half ? e + half : e - half;
+                    const float other = val[unit * dim + pe] * sc * (norm_mode >= 2 ? w[wb + pe] : 1.0f);
+                    float sn, cs;
+                    sincosf((float)pos * inv_freq[fi], &sn, &cs);
+                    sn *= rot_scale; cs *= rot_scale;
+                    o = e < half ? o * cs - other * sn : o * cs + other * sn;
+                }
+            }
+        } else if (e < vdim) {
+            o = val[QC + KC + (unit - nq - nkv) * vdim + e];
+        }
+        TA* dst;
+        if (unit < nq) {
+            dst = q_out + (size_t)t * q_out_stride + (size_t)unit * hdp + e;
+        } else {
+            const int kind = unit < nq + nkv ? 0 : 1;
+            const int kvh = kind == 0 ? unit - nq : unit - nq - nkv;
+            dst = pool + (((size_t)page * 2 + kind) * nkv + kvh) * ZLM_PAGE * hdp + (size_t)(pos % ZLM_PAGE) * hdp + e;
+        }
+        if (ZLM_CHK(dst, sizeof(TA))) *dst = from_f32<TA>(o);
+    }
+}
+
+template <typename TA>
+static void launch_attn_prep(void* q_out, int q_out_stride, const void* proj, int proj_stride, const void* conv_w, void* state,
+                             const int* token_pos, const int* token_slot, const int* token_seq, const int* seq_start,
+                             const int* cu_seqlens, const int* seq_slot, const int* block_table, int table_stride, void* pool,
+                             int T, int R, int nq, int nkv, int dim, int vdim, int hdp, int taps, int norm_mode, VecW q_w,
+                             VecW k_w, float eps, const float* inv_freq, int n_rot, float rot_scale, cudaStream_t st) {
+    const int C = (nq + nkv) * dim + nkv * vdim;
+    const size_t smem = (size_t)(C + nq + nkv + 32) * sizeof(float);
+    zlm_launch(attn_prep_kernel<TA>, dim3(T), dim3(AP_THREADS), smem, st, (TA*)q_out, q_out_stride, (const TA*)proj,
+               proj_stride, (const TA*)conv_w, (const TA*)state, token_pos, token_slot, token_seq, seq_start, cu_seqlens,
+               block_table, table_stride, (TA*)pool, nq, nkv, dim, vdim, hdp, taps, norm_mode, q_w, k_w, eps, inv_freq, n_rot,
+               rot_scale);
+    if (conv_w && taps > 1)
+        zlm_launch(conv_state_update_kernel<TA>, dim3(R, (C + 255) / 256), dim3(256), 0, st, (TA*)state, (const TA*)proj,
+                   proj_stride, seq_slot, cu_seqlens, C, taps);
+}
+
+// As zlm_conv_norm_write, with: conv_w null for no convolution; norm_mode 0 none, 1 per head without weight, 2 per
+// head with q_w / k_w [dim], 3 over all heads at once with q_w [nq*dim] / k_w [nkv*dim]; inv_freq [n_rot/2] fp32
+// (n_rot 0: no rotation); rot_scale multiplies cosines and sines.
+extern "C" int zlm_attn_prep(void* q_out, int q_out_stride, const void* proj, int proj_stride, const void* conv_w,
+                             void* state, int dtype, const int* token_pos, const int* token_slot, const int* token_seq,
+                             const int* seq_start, const int* cu_seqlens, const int* seq_slot, const int* block_table,
+                             int table_stride, void* pool, int T, int R, int nq, int nkv, int dim, int vdim, int hdp,
+                             int taps, int norm_mode, const void* q_w, const void* k_w, int w_dtype, float eps,
+                             const float* inv_freq, int n_rot, float rot_scale, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(nq > 0 && nkv > 0 && dim > 0 && vdim > 0 && hdp >= dim && hdp >= vdim, "attn_prep: heads %d/%d of %d and %d columns padded to %d",
+                nq, nkv, dim, vdim, hdp);
+    ZLM_REQUIRE(taps >= 1 && taps <= SC_MAX_TAPS, "attn_prep: %d taps (at most %d)", taps, SC_MAX_TAPS);
+    ZLM_REQUIRE(!conv_w || taps == 1 || state, "attn_prep: a convolution of %d taps needs the sequences' state", taps);
+    ZLM_REQUIRE(norm_mode >= 0 && norm_mode <= 3 && (norm_mode < 2 || (q_w && k_w)), "attn_prep: norm mode %d", norm_mode);
+    ZLM_REQUIRE(n_rot >= 0 && n_rot % 2 == 0 && n_rot <= dim && (n_rot == 0 || inv_freq), "attn_prep: rotation over %d of %d coordinates", n_rot, dim);
+    const size_t smem = (size_t)((nq + nkv) * dim + nkv * vdim + nq + nkv + 32) * sizeof(float);
+    ZLM_REQUIRE(smem <= 200 * 1024, "attn_prep: %zu bytes of channels a token", smem);
+    const VecW qw{q_w, w_dtype}, kw{k_w, w_dtype};
+    if (dtype == ZLM_DTYPE_F32) {
+        static bool big[64] = {};
+        if (smem > 48 * 1024 && !big[zlm_device_index()]) {
+            cudaFuncSetAttribute(attn_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            big[zlm_device_index()] = true;
+        }
+        launch_attn_prep<float>(q_out, q_out_stride, proj, proj_stride, conv_w, state, token_pos, token_slot, token_seq, seq_start,
+                                cu_seqlens, seq_slot, block_table, table_stride, pool, T, R, nq, nkv, dim, vdim, hdp, taps,
+                                norm_mode, qw, kw, eps, inv_freq, n_rot, rot_scale, st);
+    } else if (dtype == ZLM_DTYPE_BF16) {
+        static bool big[64] = {};
+        if (smem > 48 * 1024 && !big[zlm_device_index()]) {
+            cudaFuncSetAttribute(attn_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+            big[zlm_device_index()] = true;
+        }
+        launch_attn_prep<__nv_bfloat16>(q_out, q_out_stride, proj, proj_stride, conv_w, state, token_pos, token_slot, token_seq,
+                                        seq_start, cu_seqlens, seq_slot, block_table, table_stride, pool, T, R, nq, nkv, dim,
+                                        vdim, hdp, taps, norm_mode, qw, kw, eps, inv_freq, n_rot, rot_scale, st);
+    } else {
+        ZLM_REQUIRE(false, "attn_prep: unsupported dtype %d", dtype);
+    }
+    return zlm_check_launch("attn_prep");
+}
+
+// ---------------------------------------------------------------------------- norm, weight, gate on a recurrence's output
+// out[t][c] = o[t][c] * inv_rms(group of c) * w[...] * act(g[t][c]) * out_scale, o fp32 [T][H*V]:
+//   group 0: no norm; 1: every head of V columns by itself; 2: the whole row (all heads together);
+//   w: none, [V] shared by the heads (w_rows 0) or [H*V] (w_rows 1);  act 0 sigmoid, 1 silu, 2 no gate.
+// A block per token; sums of squares fp32 in a fixed order.
+#define NG_THREADS 256
+template <typename TA>
+__global__ void __launch_bounds__(NG_THREADS)
+norm_gate_kernel(TA* __restrict__ out, int out_stride, const float* __restrict__ o, const TA* __restrict__ g, int g_stride,
+                 int H, int V, int group, VecW w, int has_w, int w_rows, float eps, int act, float out_scale) {
+    extern __shared__ float ng_smem[];          // [H] inverse root mean squares, [32] reduction
+    pdl_trigger();
+    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int N = H * V;
+    float* inv = ng_smem;
+    float* red = ng_smem + H;
+    pdl_wait();
+    const float* op = o + (size_t)t * N;
+    if (group == 2) {
+        float ss = 0.f;
+        for (int c = tid; c < N; c += NG_THREADS) if (ZLM_CHK(op + c, 4)) ss = fmaf(op[c], op[c], ss);
+        const float tot = block_sum(ss, red);
+        if (tid < H) inv[tid] = 0.f;
+        __syncthreads();
+        const float s = 1.0f / sqrtf(tot / (float)N + eps);
+        for (int h = tid; h < H; h += NG_THREADS) inv[h] = s;
+    } else {
+        for (int h = warp; h < H; h += NG_THREADS / 32) {
+            float ss = 0.f;
+            for (int e = lane; e < V; e += 32) if (ZLM_CHK(op + h * V + e, 4)) { const float a = op[h * V + e]; ss = fmaf(a, a, ss); }
+            ss = warp_sum(ss);
+            if (lane == 0) inv[h] = group == 1 ? 1.0f / sqrtf(ss / (float)V + eps) : 1.0f;
+        }
+    }
+    __syncthreads();
+    for (int c = tid; c < N; c += NG_THREADS) {
+        const int h = c / V;
+        if (!ZLM_CHK(op + c, 4)) continue;
+        float y = op[c] * inv[h];
+        if (has_w) y *= w[w_rows ? c : c - h * V];
+        if (act != 2) {
+            const TA* gp = g + (size_t)t * g_stride + c;
+            if (!ZLM_CHK(gp, sizeof(TA))) continue;
+            const float z = to_f32(*gp);
+            const float sg = 1.0f / (1.0f + expf(-z));
+            y *= act == 1 ? z * sg : sg;
+        }
+        TA* dst = out + (size_t)t * out_stride + c;
+        if (ZLM_CHK(dst, sizeof(TA))) *dst = from_f32<TA>(y * out_scale);
+    }
+}
+
+extern "C" int zlm_norm_gate(void* out, int out_stride, const float* o, const void* g, int g_stride, int dtype, int T, int H,
+                             int V, int group, const void* w, int w_dtype, int w_rows, float eps, int act, float out_scale,
+                             cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(H > 0 && V > 0 && H <= 8192 && group >= 0 && group <= 2 && act >= 0 && act <= 2 && (act == 2 || g),
+                "norm_gate: %d heads of %d columns, group %d, activation %d", H, V, group, act);
+    const VecW vw{w, w_dtype};
+    const size_t smem = (size_t)(H + 32) * sizeof(float);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(norm_gate_kernel<float>, dim3(T), dim3(NG_THREADS), smem, st, (float*)out, out_stride, o, (const float*)g,
+                   g_stride, H, V, group, vw, w ? 1 : 0, w_rows, eps, act, out_scale);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(norm_gate_kernel<__nv_bfloat16>, dim3(T), dim3(NG_THREADS), smem, st, (__nv_bfloat16*)out, out_stride, o,
+                   (const __nv_bfloat16*)g, g_stride, H, V, group, vw, w ? 1 : 0, w_rows, eps, act, out_scale);
+    else
+        ZLM_REQUIRE(false, "norm_gate: unsupported dtype %d", dtype);
+    return zlm_check_launch("norm_gate");
+}
+
 ZLM_TRANSLATION_UNIT(short_conv)

@@ -41,7 +41,7 @@ int zlm_runtime_binding(ZlmBinding* out) {
 
 #define ZLM_UNITS(X) \
     X(attention_decode) X(attention_generic) X(attention_prefill) X(attention_prefill_tc) X(diff_attention) X(elementwise) \
-    X(gemm_bf16_mma) X(gemm_f32) X(gemm_tcgen05) X(gemv_bf16) X(latent_attention) X(latent_attention_mma) X(moe) X(moe_grouped) X(retention) X(rope_kv) X(sampling) X(short_conv) X(stream_ops)
+    X(gemm_bf16_mma) X(gemm_f32) X(gemm_tcgen05) X(gemv_bf16) X(latent_attention) X(latent_attention_mma) X(moe) X(moe_grouped) X(recurrent) X(retention) X(rope_kv) X(sampling) X(short_conv) X(stream_ops)
 #define ZLM_DECLARE(name) extern "C" int zlm_bind_##name();
 ZLM_UNITS(ZLM_DECLARE)
 

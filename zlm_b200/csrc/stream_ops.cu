@@ -258,6 +258,110 @@ extern "C" int zlm_scale_f32(float* x, long long n, float s, cudaStream_t st) {
     return zlm_check_launch("scale_f32");
 }
 
+// ---------------------------------------------------------------- out (+)= alpha a + beta b
+// The sum of two sublayers that ran side by side on one input, each with a scale of its own; fp32.
+__global__ void scaled_sum_kernel(float* __restrict__ out, const float* __restrict__ a, float alpha, const float* __restrict__ b,
+                                  float beta, size_t n, int accumulate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+        if (!ZLM_CHK(out + i, 4) || !ZLM_CHK(a + i, 4) || !ZLM_CHK(b + i, 4)) continue;
+        const float y = fmaf(alpha, a[i], beta * b[i]);
+        out[i] = accumulate ? out[i] + y : y;
+    }
+}
+
+extern "C" int zlm_scaled_sum(float* out, const float* a, float alpha, const float* b, float beta, long long n, int accumulate,
+                              cudaStream_t st) {
+    if (n <= 0) return ZLM_OK;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    zlm_launch(scaled_sum_kernel, (int)blocks, 256, 0, st, out, a, alpha, b, beta, (size_t)n, accumulate);
+    return zlm_check_launch("scaled_sum");
+}
+
+// ---------------------------------------------------------------- x = cap * tanh(x / cap)
+__global__ void softcap_f32_kernel(float* __restrict__ x, size_t n, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x)
+        if (ZLM_CHK(x + i, 4)) x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int zlm_softcap_f32(float* x, long long n, float cap, cudaStream_t st) {
+    if (n <= 0) return ZLM_OK;
+    ZLM_REQUIRE(cap > 0.f, "softcap: cap %g", (double)cap);
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    zlm_launch(softcap_f32_kernel, (int)blocks, 256, 0, st, x, (size_t)n, cap);
+    return zlm_check_launch("softcap_f32");
+}
+
+// ---------------------------------------------------------------- silu in place on the first columns of every row
+template <typename TA>
+__global__ void silu_rows_kernel(TA* __restrict__ x, int stride, int T, int cols) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t n = (size_t)T * cols;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / cols;
+        TA* p = x + t * stride + (e - t * cols);
+        if (!ZLM_CHK(p, sizeof(TA))) continue;
+        const float z = to_f32(*p);
+        *p = from_f32<TA>(z / (1.0f + expf(-z)));
+    }
+}
+
+extern "C" int zlm_silu_rows(void* x, int stride, int dtype, int T, int cols, cudaStream_t st) {
+    if (T <= 0 || cols <= 0) return ZLM_OK;
+    ZLM_REQUIRE(stride >= cols, "silu_rows: %d columns in rows of %d", cols, stride);
+    const size_t n = (size_t)T * cols;
+    int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(silu_rows_kernel<float>, blocks, 256, 0, st, (float*)x, stride, T, cols);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(silu_rows_kernel<__nv_bfloat16>, blocks, 256, 0, st, (__nv_bfloat16*)x, stride, T, cols);
+    else
+        ZLM_REQUIRE(false, "silu_rows: unsupported dtype %d", dtype);
+    return zlm_check_launch("silu_rows");
+}
+
+// ---------------------------------------------------------------- gated activation with clamped operands
+// out = g' * sigmoid(alpha g') * (u' + 1), g' = min(gate, limit), u' = clamp(up, -limit, limit); gu is [T, 2I]: gate in
+// columns [0, I), up in [I, 2I)
+template <typename TA>
+__global__ void gated_limit_kernel(TA* __restrict__ out, const TA* __restrict__ gu, int T, int I, float limit, float alpha) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t n = (size_t)T * I;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / I;
+        const int i = (int)(e - t * I);
+        if (!ZLM_CHK(&gu[t * 2 * I + i], sizeof(TA)) || !ZLM_CHK(&gu[t * 2 * I + I + i], sizeof(TA)) ||
+            !ZLM_CHK(&out[e], sizeof(TA)))
+            continue;
+        const float g = fminf(to_f32(gu[t * 2 * I + i]), limit);
+        const float u = fminf(fmaxf(to_f32(gu[t * 2 * I + I + i]), -limit), limit);
+        out[e] = from_f32<TA>(g / (1.0f + expf(-alpha * g)) * (u + 1.0f));
+    }
+}
+
+extern "C" int zlm_gated_limit(void* out, const void* gu, int dtype, int T, int I, float limit, float alpha, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(T > 0 && I > 0 && limit > 0.f, "gated_limit: bad sizes T=%d I=%d limit=%g", T, I, (double)limit);
+    const size_t n = (size_t)T * I;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == ZLM_DTYPE_F32)
+        zlm_launch(gated_limit_kernel<float>, blocks, 256, 0, st, (float*)out, (const float*)gu, T, I, limit, alpha);
+    else if (dtype == ZLM_DTYPE_BF16)
+        zlm_launch(gated_limit_kernel<__nv_bfloat16>, blocks, 256, 0, st, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, T, I,
+                   limit, alpha);
+    else
+        ZLM_REQUIRE(false, "gated_limit: unsupported dtype %d", dtype);
+    return zlm_check_launch("gated_limit");
+}
+
 // ---------------------------------------------------------------- one gate number per head
 // x [T, heads, V] (any token and head strides) *= sigmoid(g[t, h]); a warp per (token, head)
 template <typename TA>

@@ -794,6 +794,158 @@ class CudaKernels:
             return
         self._call("zlm_retention", *head, *tail[:-1], c_int(int(getattr(plan, "max_new", 0) or 0)), tail[-1])
 
+    def attn_prep(self, q_out: torch.Tensor, proj: torch.Tensor, conv_w: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                  plan, block_table: torch.Tensor, pool: torch.Tensor, nq: int, nkv: int, dim: int, vdim: int, taps: int,
+                  norm: str, q_w: Optional[torch.Tensor], k_w: Optional[torch.Tensor], eps: float,
+                  inv_freq: Optional[torch.Tensor], n_rot: int, rot_scale: float = 1.0) -> None:
+        """``conv_norm_write`` in its general form: the convolution is optional (``conv_w`` None), the norm of q and k is
+        "none", "unit" (per head, no weight), "head" (per head, weights ``q_w`` / ``k_w`` [dim] shared by the heads) or
+        "row" (over all heads of q, and of k, at once, weights [nq*dim] / [nkv*dim]), and the first ``n_rot`` coordinates
+        of every q and k head are rotated (i against i + n_rot/2) by pos * inv_freq[i], cosines and sines times
+        ``rot_scale``."""
+        T = proj.shape[0]
+        hdp = pool.shape[-1]
+        C = (nq + nkv) * dim + nkv * vdim
+        mode = {"none": 0, "unit": 1, "head": 2, "row": 3}[norm]
+        assert proj.shape[1] >= C and proj.stride(1) == 1 and q_out.shape == (T, nq * hdp) and q_out.stride(1) == 1
+        assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hdp) and pool.is_contiguous() and block_table.dtype == torch.int32
+        assert proj.dtype == q_out.dtype == pool.dtype
+        if conv_w is not None:
+            assert conv_w.shape == (C, taps) and conv_w.is_contiguous() and conv_w.dtype == proj.dtype
+            if taps > 1:
+                assert state is not None and tuple(state.shape[1:]) == (taps - 1, C) and state.is_contiguous() and state.dtype == proj.dtype
+        else:
+            taps = 1
+        if mode >= 2:
+            want_q, want_k = ((dim,), (dim,)) if mode == 2 else ((nq * dim,), (nkv * dim,))
+            assert q_w is not None and k_w is not None and tuple(q_w.shape) == want_q and tuple(k_w.shape) == want_k
+            assert q_w.dtype == k_w.dtype and q_w.is_contiguous() and k_w.is_contiguous()
+        if inv_freq is not None and n_rot:
+            assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot and n_rot <= dim
+        else:
+            n_rot = 0
+        self._call("zlm_attn_prep", self._p(q_out), c_int(q_out.stride(0)), self._p(proj), c_int(proj.stride(0)),
+                   self._p(conv_w), self._p(state if (conv_w is not None and taps > 1) else None), c_int(_dt(proj)),
+                   self._p(plan.token_pos), self._p(plan.token_slot), self._p(plan.token_seq), self._p(plan.seq_start),
+                   self._p(plan.cu_seqlens), self._p(plan.seq_slot), self._p(block_table), c_int(block_table.stride(0)),
+                   self._p(pool), c_int(T), c_int(plan.R), c_int(nq), c_int(nkv), c_int(dim), c_int(vdim), c_int(hdp),
+                   c_int(taps), c_int(mode), self._p(q_w if mode >= 2 else None), self._p(k_w if mode >= 2 else None),
+                   c_int(_dt(q_w) if mode >= 2 else F32), c_float(eps), self._p(inv_freq if n_rot else None), c_int(n_rot),
+                   c_float(rot_scale), self._stream())
+
+    def norm_gate(self, out: torch.Tensor, o: torch.Tensor, g: Optional[torch.Tensor], heads: int, v_dim: int, group: str,
+                  weight: Optional[torch.Tensor], eps: float, act: str, out_scale: float = 1.0) -> None:
+        """out[t, c] = o[t, c] / rms(group of c) * weight * act(g[t, c]) * out_scale for o fp32 [T, heads*v_dim]: ``group``
+        "none", "head" (every head of v_dim columns by itself) or "row" (all heads together); ``weight`` None, [v_dim]
+        (shared by the heads) or [heads*v_dim]; ``act`` "sigmoid", "silu" or "none" (no gate)."""
+        T, N = o.shape
+        assert N == heads * v_dim and o.dtype == torch.float32 and o.is_contiguous()
+        assert out.shape == (T, N) and out.stride(1) == 1
+        a = {"sigmoid": 0, "silu": 1, "none": 2}[act]
+        if a != 2:
+            assert g is not None and g.shape == (T, N) and g.stride(1) == 1 and g.dtype == out.dtype
+        w_rows = 0
+        if weight is not None:
+            assert weight.is_contiguous() and weight.numel() in (v_dim, N)
+            w_rows = 1 if (weight.numel() == N and heads > 1) else 0
+        self._call("zlm_norm_gate", self._p(out), c_int(out.stride(0)), self._p(o), self._p(g if a != 2 else None),
+                   c_int(g.stride(0) if a != 2 else 0), c_int(_dt(out)), c_int(T), c_int(heads), c_int(v_dim),
+                   c_int({"none": 0, "head": 1, "row": 2}[group]), self._p(weight),
+                   c_int(_dt(weight) if weight is not None else F32), c_int(w_rows), c_float(eps), c_int(a),
+                   c_float(out_scale), self._stream())
+
+    # -- recurrent mixers (see csrc/recurrent.cu) ---------------------------------------------------------------
+    def rglru(self, out: torch.Tensor, proj: torch.Tensor, x_off: int, y_off: int, bx: Optional[torch.Tensor],
+              by: Optional[torch.Tensor], conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], a_r: torch.Tensor,
+              a_i: torch.Tensor, c_r: Optional[torch.Tensor], c_i: Optional[torch.Tensor], lam: torch.Tensor, c_decay: float,
+              state: torch.Tensor, plan, width: int, blocks: int, taps: int, out_scale: float = 1.0) -> None:
+        """The real-gated linear recurrent unit behind its convolution.  ``proj`` [T, >= 2*width] holds the x branch from
+        column x_off and the y branch from y_off, without their biases ``bx`` / ``by``; u = conv(x + bx) + conv_b (``conv_w``
+        [width, taps]); r, i = sigmoid(A u_b + c) with ``a_r`` / ``a_i`` [blocks, width/blocks, width/blocks] (out, in) on the
+        blocks of u; a = exp(-c_decay * r * softplus(lam)); S = a S + sqrt(1 - a^2) i u; out [T, width] = S * gelu_tanh(y + by)
+        * out_scale in the compute dtype.  ``state`` [slots, taps, width] fp32: row 0 is S, the others the newest x + bx."""
+        T = proj.shape[0]
+        W = width
+        dt = proj.dtype
+        assert out.shape == (T, W) and out.stride(1) == 1 and out.dtype == dt and proj.stride(1) == 1
+        assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (taps, W) and state.is_contiguous()
+        bs = W // blocks
+        assert conv_w.shape == (W, taps) and conv_w.is_contiguous() and conv_w.dtype == dt
+        for m in (a_r, a_i):
+            assert m.shape == (blocks, bs, bs) and m.is_contiguous() and m.dtype == dt
+        for v in (bx, by, conv_b, c_r, c_i, lam):
+            assert v is None or (v.numel() == W and v.is_contiguous() and v.dtype == dt)
+        u = plan.scratch("rglru.u", (T, W), torch.float32)
+        zr = plan.scratch("rglru.zr", (T, W), torch.float32)
+        zi = plan.scratch("rglru.zi", (T, W), torch.float32)
+        self._call("zlm_rglru", self._p(out), c_int(out.stride(0)), self._p(u), self._p(zr), self._p(zi), self._p(proj),
+                   c_int(proj.stride(0)), c_int(x_off), c_int(y_off), self._p(bx), self._p(by), self._p(conv_w), self._p(conv_b),
+                   self._p(a_r), self._p(a_i), self._p(c_r), self._p(c_i), self._p(lam), c_float(c_decay), self._p(state),
+                   c_int(_dt(proj)), self._p(plan.token_pos), self._p(plan.token_slot), self._p(plan.token_seq),
+                   self._p(plan.seq_start), self._p(plan.cu_seqlens), self._p(plan.seq_slot), c_int(T), c_int(plan.R), c_int(W),
+                   c_int(blocks), c_int(taps), c_float(out_scale), self._stream())
+
+    def lowrank_decay(self, alpha: torch.Tensor, proj: torch.Tensor, lo_off: int, w2: torch.Tensor, b: Optional[torch.Tensor],
+                      tau: float) -> None:
+        """alpha [T, C] fp32 = sigmoid(w2 lo + b)^(1/tau), lo = ``rank`` columns of proj from lo_off on, w2 [C, rank]."""
+        T = proj.shape[0]
+        C, rank = w2.shape
+        assert alpha.shape == (T, C) and alpha.dtype == torch.float32 and alpha.is_contiguous() and proj.stride(1) == 1
+        assert w2.is_contiguous() and w2.dtype == proj.dtype and (b is None or (b.numel() == C and b.dtype == proj.dtype and b.is_contiguous()))
+        self._call("zlm_lowrank_decay", self._p(alpha), self._p(proj), c_int(proj.stride(0)), c_int(lo_off), self._p(w2),
+                   self._p(b), c_int(_dt(proj)), c_int(T), c_int(C), c_int(rank), c_float(tau), self._stream())
+
+    def linear_attention(self, o: torch.Tensor, proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
+                         alpha: Optional[torch.Tensor], head_decay: Optional[torch.Tensor], state: torch.Tensor, plan,
+                         heads: int, dim: int, v_dim: int, q_scale: float = 1.0) -> None:
+        """o [T, heads*v_dim] fp32 = S_t^T q_t with S_t = diag(alpha_t) S_(t-1) + k_t v_t^T per head; q (times ``q_scale``),
+        k, v are columns of ``proj`` from q_off, k_off, v_off on; ``alpha`` [T, heads*dim] fp32 gives a decay per token and
+        key channel, or ``head_decay`` [heads] fp32 one per head; ``state`` [slots, heads, dim, v_dim] fp32."""
+        T = proj.shape[0]
+        assert o.shape == (T, heads * v_dim) and o.dtype == torch.float32 and o.is_contiguous() and proj.stride(1) == 1
+        assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, v_dim) and state.is_contiguous()
+        if alpha is not None:
+            assert alpha.shape == (T, heads * dim) and alpha.dtype == torch.float32 and alpha.is_contiguous()
+        else:
+            assert head_decay is not None and head_decay.dtype == torch.float32 and head_decay.numel() == heads
+        self._call("zlm_linear_attention", self._p(o), self._p(proj), c_int(proj.stride(0)), c_int(q_off), c_int(k_off),
+                   c_int(v_off), self._p(alpha), self._p(head_decay if alpha is None else None), self._p(state), c_int(_dt(proj)),
+                   self._p(plan.seq_slot), self._p(plan.cu_seqlens), c_int(T), c_int(plan.R), c_int(heads), c_int(dim),
+                   c_int(v_dim), c_float(q_scale), self._stream())
+
+    def scaled_sum(self, out: torch.Tensor, a: torch.Tensor, alpha: float, b: torch.Tensor, beta: float,
+                   accumulate: bool = True) -> None:
+        """out += alpha a + beta b (or out = ..., also when ``out`` is the tensor that ``expect_blank`` named); fp32
+        tensors of one shape."""
+        assert out.dtype == a.dtype == b.dtype == torch.float32 and out.shape == a.shape == b.shape
+        assert out.is_contiguous() and a.is_contiguous() and b.is_contiguous()
+        blank = self._blank
+        if blank is not None and blank.data_ptr() == out.data_ptr() and tuple(blank.shape) == tuple(out.shape):
+            self._blank = None
+            accumulate = False
+        self._call("zlm_scaled_sum", self._p(out), self._p(a), c_float(alpha), self._p(b), c_float(beta),
+                   ctypes.c_longlong(out.numel()), c_int(1 if accumulate else 0), self._stream())
+
+    def softcap_(self, x: torch.Tensor, cap: float) -> None:
+        """x = cap * tanh(x / cap) for a contiguous fp32 tensor (logits)."""
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        if self._candidates is not None and self._candidates[0] == x.data_ptr():
+            self._candidates = None
+        self._call("zlm_softcap_f32", self._p(x), ctypes.c_longlong(x.numel()), c_float(cap), self._stream())
+
+    def silu_rows(self, x: torch.Tensor, cols: int) -> None:
+        """x[:, :cols] = silu(x[:, :cols]) in place."""
+        T = x.shape[0]
+        assert x.stride(1) == 1 and 0 <= cols <= x.shape[1]
+        self._call("zlm_silu_rows", self._p(x), c_int(x.stride(0)), c_int(_dt(x)), c_int(T), c_int(cols), self._stream())
+
+    def gated_limit(self, out: torch.Tensor, gu: torch.Tensor, limit: float, alpha: float) -> None:
+        """out[t, i] = g sigmoid(alpha g) (u + 1) with g = min(gu[t, i], limit), u = clamp(gu[t, I + i], -limit, limit)."""
+        T, I = out.shape
+        assert gu.shape == (T, 2 * I) and gu.dtype == out.dtype and out.is_contiguous() and gu.is_contiguous()
+        self._call("zlm_gated_limit", self._p(out), self._p(gu), c_int(_dt(out)), c_int(T), c_int(I), c_float(limit),
+                   c_float(alpha), self._stream())
+
     # -- latent attention (see csrc/latent_attention.cu) --------------------
     def latent_prep(self, q: torch.Tensor, q_rot: torch.Tensor, dkv: Optional[torch.Tensor],
                     c_weight: Optional[torch.Tensor], eps: float,
@@ -990,6 +1142,13 @@ class CudaKernels:
         first through this class has it cleared then, so the word is never wrong."""
         self._blank = t
 
+    def swap_blank(self, t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+        """``expect_blank(t)`` that hands back the tensor named before and not yet used up (None if none): for a part that
+        runs other parts on blank rows of its own while a word on its own output is still pending, and puts that word
+        back afterwards."""
+        was, self._blank = self._blank, t
+        return was
+
     # -- differential attention (see csrc/diff_attention.cu) --------------------------------------------------
     def diff_prep(self, q_out: torch.Tensor, proj: torch.Tensor, q_w: torch.Tensor, k_w: torch.Tensor, eps: float,
                   inv_freq: Optional[torch.Tensor], n_rot: int, token_pos: torch.Tensor, token_slot: torch.Tensor,
@@ -1030,12 +1189,13 @@ class CudaKernels:
     def moe_route(self, idx: torch.Tensor, wgt: torch.Tensor, x: torch.Tensor, w_router: torch.Tensor, top: int,
                   gate: Optional[torch.Tensor] = None, w_gate: Optional[torch.Tensor] = None,
                   score: str = "sigmoid", renormalize: bool = False, correction: Optional[torch.Tensor] = None,
-                  groups: int = 1, keep: int = 1, weight_scale: float = 1.0) -> None:
+                  groups: int = 1, keep: int = 1, weight_scale: float = 1.0, group_top: int = 1) -> None:
         """idx / wgt [T, top]: the experts with the largest scores of W_router x (fp32 logits; ``score``
         "sigmoid" or "softmax") and those scores (divided by their sum if ``renormalize``); gate [T] =
         sigmoid(w_gate . x) where a shared expert has a gate.  ``correction`` (fp32 [E]) is added to the scores for the
         choice only; the experts form ``groups`` equal groups of neighbours of which the ``keep`` with the largest best
-        choice score can be chosen; the weights are the scores times ``weight_scale``."""
+        choice score (``group_top`` 2: the largest sum of its two best choice scores) can be chosen; the weights are the
+        scores times ``weight_scale``."""
         T, K = x.shape
         E = w_router.shape[0]
         assert w_router.shape == (E, K) and w_router.is_contiguous() and w_router.dtype == x.dtype and x.stride(1) == 1
@@ -1047,17 +1207,18 @@ class CudaKernels:
         self._call("zlm_moe_route", self._p(idx), self._p(wgt), self._p(gate if w_gate is not None else None), self._p(x),
                    c_int(x.stride(0)), self._p(w_router), self._p(w_gate), c_int(_dt(x)), c_int(T), c_int(E), c_int(K),
                    c_int(top), c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0),
-                   *self._route_extras(correction, E, groups, keep, weight_scale), self._stream())
+                   *self._route_extras(correction, E, groups, keep, weight_scale, group_top), self._stream())
 
-    def _route_extras(self, correction, E, groups, keep, weight_scale):
+    def _route_extras(self, correction, E, groups, keep, weight_scale, group_top=1):
         if correction is not None:
             assert correction.dtype == torch.float32 and correction.shape == (E,) and correction.is_contiguous()
-        return self._p(correction), c_int(groups), c_int(keep), c_float(weight_scale)
+        assert group_top in (1, 2)
+        return self._p(correction), c_int(groups), c_int(keep), c_int(group_top), c_float(weight_scale)
 
     def moe_choose(self, idx: torch.Tensor, wgt: torch.Tensor, logits: torch.Tensor, experts: int, top: int,
                    gate: Optional[torch.Tensor] = None, score: str = "sigmoid", renormalize: bool = False,
                    correction: Optional[torch.Tensor] = None, groups: int = 1, keep: int = 1,
-                   weight_scale: float = 1.0) -> None:
+                   weight_scale: float = 1.0, group_top: int = 1) -> None:
         """``moe_route``'s choice from fp32 logits [T, experts (+ 1)] that a product left (column ``experts`` is the
         shared expert's gate logit if ``gate`` is given)."""
         T = logits.shape[0]
@@ -1067,7 +1228,7 @@ class CudaKernels:
         self._call("zlm_moe_choose", self._p(idx), self._p(wgt), self._p(gate), self._p(logits), c_int(logits.stride(0)),
                    c_int(T), c_int(experts), c_int(top), c_int(1 if gate is not None else 0),
                    c_int({"sigmoid": 0, "softmax": 1}[score]), c_int(1 if renormalize else 0),
-                   *self._route_extras(correction, experts, groups, keep, weight_scale), self._stream())
+                   *self._route_extras(correction, experts, groups, keep, weight_scale, group_top), self._stream())
 
     _ACT_KINDS = {"relu2": 0, "swiglu": 1, "swiglu_interleaved": 2}
 

@@ -1,6 +1,6 @@
 from .base import (CacheRequest, CacheView, FeedForward, LayerIO, Mixer, Norm, ParamSpec, Part,
                    PositionEncoding, Runtime, StateRequest, StepContext, Workspace)
-from . import norm, rope, attention, latent_attention, conv_attention, diff_attention, retention, mlp, moe, block, embedding   # register the built-in parts
+from . import norm, rope, attention, latent_attention, conv_attention, diff_attention, retention, recurrent, parallel, mlp, moe, block, embedding   # register the built-in parts
 from .model import DecoderModel
 
 __all__ = ["CacheRequest", "CacheView", "FeedForward", "LayerIO", "Mixer", "Norm", "ParamSpec", "Part",

@@ -38,6 +38,8 @@ class GQAAttention(Mixer):
         kind = position.pop("kind")
         self.position = lookup(POSITION_ENCODINGS, "position encoding", kind)(**position)
         self.Q, self.KV = self.nq * self.hd, self.nkv * self.hd
+        if getattr(self.position, "mscale", 1.0) != 1.0:
+            raise ValueError("this mixer's kernels do not take a rotation with scaled frequencies")
 
     # ---- declarations -----------------------------------------------------
     def param_specs(self) -> Dict[str, ParamSpec]:

@@ -34,11 +34,21 @@ class ParamSpec:
     init:  how the random-weights mode fills it ("normal": N(0, 0.02);
            "one_plus_normal": 1 + N(0, 0.02); "zeros").
     ignorable: may be present in the file although the part does not use it.
+    shape: a dimension of -1 is one that the checkpoint gives (a low rank that no configuration key names); the part
+           reads it off the tensor in ``bind``.  ``free_size`` is what the random-weights mode makes of it.
     """
     shape: Tuple[int, ...]
     kind: str = "matrix"
     init: str = "normal"
     ignorable: bool = False
+    free_size: int = 16
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w == -1 or w == s for w, s in zip(self.shape, shape))
+
+    def concrete_shape(self) -> Tuple[int, ...]:
+        return tuple(self.free_size if s == -1 else s for s in self.shape)
 
 
 @dataclass(frozen=True)
@@ -123,7 +133,7 @@ class CacheView:
 class LayerIO:
     """What one schedule entry owns beside its weights."""
     cache: Optional[CacheView] = None
-    state: Optional[torch.Tensor] = None     # [slots, *StateRequest.shape]
+    state: Any = None     # [slots, *StateRequest.shape]; a tuple of such tensors where the mixer asked with a tuple of requests
 
 
 @dataclass

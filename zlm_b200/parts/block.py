@@ -7,10 +7,13 @@ into the stream themselves, so the last projection of each can carry the add.
 ``sublayer_norm``: h = h + norm(mixer(h)); h = h + norm(ffn(h)): the norm stands on the sublayer's *output*, the
 sublayers read the stream itself.  The norm may carry a scale per coordinate of its own (``rms_norm`` with
 ``layer_scale``); norm, scale and the residual add are one kernel in fp32.
+
+``sandwich_norm``: h = h + post1(mixer(pre1(h))); h = h + post2(ffn(pre2(h))): a norm on what a sublayer reads and
+another on what it gives.
 """
 from __future__ import annotations
 
-from typing import Dict
+from typing import Dict, Optional
 
 import torch
 
@@ -133,3 +136,59 @@ class SublayerNormBlock(Part):
         self._sublayer(self.mixer, self.mixer_norm, hidden, lambda x, y: self.mixer.forward(x, y, ctx, io), ctx)
         if not getattr(self.ffn, "is_identity", False):
             self._sublayer(self.ffn, self.ffn_norm, hidden, lambda x, y: self.ffn.forward(x, y, ctx), ctx)
+
+
+@register_arrangement("sandwich_norm")
+class SandwichNormBlock(Part):
+    """x <- x + post1(mixer(pre1(x))), then x <- x + post2(ffn(pre2(x))).  The sublayer reads the normed rows (compute
+    dtype) and "adds its result" into a scratch row per token that counts as zeros (``expect_blank``); the second norm
+    norms that row and adds it into the fp32 stream in one kernel (``Norm.add_into``)."""
+
+    def __init__(self, hidden_size: int, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm,
+                 mixer_post_norm: Norm, feed_forward_post_norm: Optional[Norm] = None):
+        self.hidden = int(hidden_size)
+        self.mixer, self.ffn = mixer, feed_forward
+        self.mixer_norm, self.ffn_norm = mixer_norm, feed_forward_norm
+        self.mixer_post, self.ffn_post = mixer_post_norm, feed_forward_post_norm
+        if self.ffn_post is None and not getattr(self.ffn, "is_identity", False):
+            raise ValueError("sandwich_norm: a feed-forward without a norm on its output")
+
+    def children(self) -> Dict[str, Part]:
+        c = {"mixer": self.mixer, "feed_forward": self.ffn, "mixer_norm": self.mixer_norm,
+             "feed_forward_norm": self.ffn_norm, "mixer_post_norm": self.mixer_post}
+        if self.ffn_post is not None:
+            c["feed_forward_post_norm"] = self.ffn_post
+        return c
+
+    graph_safe = PreNormBlock.graph_safe
+    prefers_plain_launches = PreNormBlock.prefers_plain_launches
+    step_key = PreNormBlock.step_key
+
+    def first_norm_weight(self):
+        return None             # (the block before is told nothing: this block's norms are always run)
+
+    def _sublayer(self, pre: Norm, post: Norm, hidden: torch.Tensor, run) -> None:
+        rt, k = self.rt, self.rt.k
+        self.finish_products()
+        x = rt.ws.get("block.normed", hidden.shape, rt.dtype)
+        pre.forward(x, hidden)
+        y = rt.ws.get("block.sublayer_out", hidden.shape, torch.float32)
+        blank = getattr(k, "expect_blank", None)
+        if blank is not None:
+            blank(y)
+        else:
+            y.zero_()
+        run(x, y)
+        if blank is not None:
+            blank(None)
+        post.add_into(hidden, y)
+
+    def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
+        ctx.extras.pop("stream.rounded", None)
+        for word in ("expect_norm", "norm_output_read_by_products"):
+            say = getattr(self.rt.k, word, None)
+            if say is not None:
+                say(None if word == "expect_norm" else False)
+        self._sublayer(self.mixer_norm, self.mixer_post, hidden, lambda x, y: self.mixer.forward(x, y, ctx, io))
+        if not getattr(self.ffn, "is_identity", False):
+            self._sublayer(self.ffn_norm, self.ffn_post, hidden, lambda x, y: self.ffn.forward(x, y, ctx))

@@ -95,10 +95,11 @@ class TokenEmbedding(Part):
 
 @register_head("lm_head")
 class LMHead(Part):
-    def __init__(self, vocab_size: int, hidden_size: int, tied: bool, logit_scale: float = 1.0):
-        """``logit_scale``: the logits are multiplied by it (in fp32, after the product)."""
+    def __init__(self, vocab_size: int, hidden_size: int, tied: bool, logit_scale: float = 1.0, softcap: float = 0.0):
+        """``logit_scale``: the logits are multiplied by it (in fp32, after the product).  ``softcap``: the logits
+        become softcap * tanh(logits / softcap) (0: no cap)."""
         self.vocab, self.hidden, self.tied = int(vocab_size), int(hidden_size), bool(tied)
-        self.logit_scale = float(logit_scale)
+        self.logit_scale, self.softcap = float(logit_scale), float(softcap)
         self.weight: Optional[torch.Tensor] = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -119,3 +120,5 @@ class LMHead(Part):
         self.rt.k.linear(logits, x, self.weight)
         if self.logit_scale != 1.0:
             self.rt.k.scale_(logits, self.logit_scale)
+        if self.softcap > 0.0:
+            self.rt.k.softcap_(logits, self.softcap)

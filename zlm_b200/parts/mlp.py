@@ -18,14 +18,19 @@ from .base import FeedForward, ParamSpec, StepContext
 class SwiGLU(FeedForward):
     reads_input_by_products = True       # x goes into the gate/up product and nowhere else
 
-    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+    def __init__(self, hidden_size: int, intermediate_size: int, activation: str = "silu", limit: float = 0.0,
+                 alpha: float = 1.702):
         """``activation``: what the gate passes through, "silu" or "gelu_tanh"
-        (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
+        (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))), or "swish_limit": with g = min(gate, limit) and
+        u = clamp(up, -limit, limit) the product of the two halves is g sigmoid(alpha g) (u + 1)."""
         self.hidden = int(hidden_size)
         self.inter = int(intermediate_size)
-        if activation not in ("silu", "gelu_tanh"):
+        if activation not in ("silu", "gelu_tanh", "swish_limit"):
             raise ValueError(f"gated feed-forward: activation={activation!r}")
         self.act = activation
+        self.limit, self.alpha = float(limit), float(alpha)
+        if activation == "swish_limit" and not self.limit > 0:
+            raise ValueError(f"gated feed-forward: limit={limit!r}")
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
@@ -69,6 +74,8 @@ class SwiGLU(FeedForward):
             k.linear(gu, x, self.w_gu)
             if self.act == "silu":
                 k.swiglu(act, gu)
+            elif self.act == "swish_limit":
+                k.gated_limit(act, gu, self.limit, self.alpha)
             else:
                 k.gated_act(act, gu, self.act)
         k.linear(residual, act, self.w_down, accumulate=True, defer=True)      # a norm reads the stream next

@@ -38,11 +38,19 @@ class DecoderModel:
             ffn = _build(FEED_FORWARDS, "feed-forward", ls.feed_forward, hidden_size=H)
             n1 = _build(NORMS, "norm", ls.mixer_norm, size=H)
             n2 = _build(NORMS, "norm", ls.feed_forward_norm, size=H)
-            block = lookup(ARRANGEMENTS, "block arrangement", ls.arrangement)(
-                hidden_size=H, mixer=mixer, feed_forward=ffn, mixer_norm=n1, feed_forward_norm=n2)
+            # (norms on the sublayers' outputs, for the arrangements that have them)
+            post = {name: (_build(NORMS, "norm", ps, size=H), ps)
+                    for name, ps in (("mixer_post_norm", ls.mixer_post_norm), ("feed_forward_post_norm", ls.feed_forward_post_norm))
+                    if ps is not None}
+            try:
+                block = lookup(ARRANGEMENTS, "block arrangement", ls.arrangement)(
+                    hidden_size=H, mixer=mixer, feed_forward=ffn, mixer_norm=n1, feed_forward_norm=n2,
+                    **{name: part for name, (part, _) in post.items()})
+            except TypeError as e:
+                raise ConfigError(f"block arrangement '{ls.arrangement}': {e}") from None
             self.blocks.append(block)
             self._owners += [(mixer, ls.mixer), (ffn, ls.feed_forward), (n1, ls.mixer_norm),
-                             (n2, ls.feed_forward_norm)]
+                             (n2, ls.feed_forward_norm)] + list(post.values())
         self.rt: Optional[Runtime] = None
 
     # ---- weights ------------------------------------------------------------

@@ -15,7 +15,8 @@ Options that other designs use:
     ``correction``             a vector (tensor ``correction``) added to the scores for the choice only; the weights
                                are the scores without it
     ``groups``, ``keep``       the experts form ``groups`` equal groups of neighbours; a group's mark is its largest
-                               choice score, and only experts of the ``keep`` best groups can be chosen
+                               choice score (``group_mark="top2_sum"``: the sum of its two largest), and only
+                               experts of the ``keep`` best groups can be chosen
     ``route_scale``            multiplies the weights
     ``identity``               the last ``identity`` of the router's num_experts + identity outputs are experts
                                without tensors whose output is their input (times the weight); they take part in
@@ -51,7 +52,7 @@ class RoutedExperts(FeedForward):
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, expert_ff: int, shared_ff: int = 0,
                  shared_gate: bool = True, score: str = "sigmoid", renormalize: bool = False,
                  weight_on: str = "input", activation: str = "relu2", correction: bool = False, groups: int = 1,
-                 keep: int = 1, route_scale: float = 1.0, identity: int = 0):
+                 keep: int = 1, route_scale: float = 1.0, identity: int = 0, group_mark: str = "max"):
         self.hidden, self.E, self.top, self.F = int(hidden_size), int(num_experts), int(top_k), int(expert_ff)
         self.SF, self.shared_gate = int(shared_ff), bool(shared_gate) and int(shared_ff) > 0
         if not 0 < self.top <= self.E + int(identity):
@@ -63,6 +64,9 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"routed experts: activation={activation!r}")
         self.activation, self.has_correction = activation, bool(correction)
         self.groups, self.keep, self.route_scale, self.identity = int(groups), int(keep), float(route_scale), int(identity)
+        if group_mark not in ("max", "top2_sum"):
+            raise ValueError(f"routed experts: group_mark={group_mark!r}")
+        self.group_top = 2 if group_mark == "top2_sum" else 1
         self.routes = self.E + self.identity                       # the router's outputs
         if self.identity < 0 or self.top > self.routes:
             raise ValueError(f"routed experts: top_k={self.top} of {self.routes} router outputs, {self.identity} of them identities")
@@ -147,10 +151,10 @@ class RoutedExperts(FeedForward):
             logits = rt.ws.get("moe.logits", (T, self.w_route.shape[0]), torch.float32)
             k.linear(logits, x, self.w_route)
             k.moe_choose(idx, wgt, logits, self.routes, self.top, gate, self.score, self.renormalize, self.correction,
-                         self.groups, self.keep, self.route_scale)
+                         self.groups, self.keep, self.route_scale, self.group_top)
         else:
             k.moe_route(idx, wgt, x, self.w_router, self.top, gate, self.w_sg, self.score, self.renormalize,
-                        self.correction, self.groups, self.keep, self.route_scale)
+                        self.correction, self.groups, self.keep, self.route_scale, self.group_top)
         grouped = self.up_layout == "swiglu_interleaved" or (self.activation == "relu2" and not self.identity)
         if (grouped and T > 16 and rt.dtype == torch.bfloat16 and self.F % 8 == 0 and self.hidden % 8 == 0
                 and x.stride(0) % 8 == 0 and hasattr(k, "moe_grouped")):

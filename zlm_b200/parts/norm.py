@@ -4,6 +4,8 @@ y = (x * 1/sqrt(mean(x^2) + eps)) * w, weight used as it is
 (src/kernels/transformer/norm.zig:4-37).  ``scalar``: the checkpoint holds one gain for the whole
 row (a tensor without dimensions) instead of a weight per coordinate.  ``layer_scale``: a second vector ``scale``
 multiplies the normed row coordinate by coordinate (a layer's learned scale on its sublayer's output).
+``one_plus``: the checkpoint stores the weight around zero and the row is multiplied by 1 + w (the sum is made once,
+in fp32, when the weights are bound).
 """
 from __future__ import annotations
 
@@ -19,8 +21,10 @@ from .base import Norm, ParamSpec
 class RMSNorm(Norm):
     reads_stream_by_kernel = True
 
-    def __init__(self, size: int, eps: float, scalar: bool = False, layer_scale: bool = False):
+    def __init__(self, size: int, eps: float, scalar: bool = False, layer_scale: bool = False, one_plus: bool = False):
         self.size = int(size)
+        self.one_plus = bool(one_plus)
+        self.stored: Optional[torch.Tensor] = None
         self.eps = float(eps)
         self.scalar = bool(scalar)
         self.layer_scale = bool(layer_scale)
@@ -30,22 +34,26 @@ class RMSNorm(Norm):
         self.reads_stream_by_kernel = not self.layer_scale      # (with a scale the plain norm kernel is not the whole norm)
 
     def param_specs(self) -> Dict[str, ParamSpec]:
-        s = {"weight": ParamSpec(() if self.scalar else (self.size,), kind="vector", init="one_plus_normal")}
+        s = {"weight": ParamSpec(() if self.scalar else (self.size,), kind="vector",
+                                 init="normal" if self.one_plus else "one_plus_normal")}
         if self.layer_scale:
             s["scale"] = ParamSpec((self.size,), kind="vector", init="one_plus_normal")
         return s
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         self.weight = params["weight"]
+        if self.one_plus:
+            self.stored = self.weight
+            self.weight = (1.0 + self.stored.float()).contiguous()
         self.scale = params.get("scale")
         if self.scalar:
             # the kernels (and the products that fold a norm in) read a weight per coordinate: the one
             # gain, widened to 32 bits (exact), repeated along the row
-            self.gain = self.weight
-            self.weight = self.gain.float().reshape(1).expand(self.size).contiguous()
+            self.gain = self.stored if self.one_plus else self.weight
+            self.weight = self.weight.float().reshape(1).expand(self.size).contiguous()
 
     def tensors(self) -> Dict[str, torch.Tensor]:
-        out = {"weight": self.gain if self.scalar else self.weight}
+        out = {"weight": self.gain if self.scalar else (self.stored if self.one_plus else self.weight)}
         if self.layer_scale:
             out["scale"] = self.scale
         return out

@@ -63,7 +63,7 @@ def check_names(folder: str, expected: Mapping[str, ParamSpec], shapes: Mapping[
     missing = [n for n, p in expected.items() if n not in shapes and not p.ignorable]
     unexpected = [n for n in shapes if n not in expected]
     wrong = [(n, tuple(shapes[n]), tuple(p.shape)) for n, p in expected.items()
-             if n in shapes and tuple(shapes[n]) != tuple(p.shape) and not p.ignorable]
+             if n in shapes and not p.fits(shapes[n]) and not p.ignorable]
     bad_dt = []
     for n, p in expected.items():
         if n in dtypes and not p.ignorable:
@@ -87,7 +87,7 @@ def load_weights(folder: str, expected: Mapping[str, ParamSpec], compute: torch.
     check_names(folder, expected, shapes, dtypes)
     out: Dict[str, torch.Tensor] = {}
     for name, spec in expected.items():
-        if name not in where or (spec.ignorable and tuple(shapes[name]) != tuple(spec.shape)):
+        if name not in where or (spec.ignorable and not spec.fits(shapes[name])):
             continue
         if spec.ignorable:
             continue

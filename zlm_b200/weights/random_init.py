@@ -28,14 +28,15 @@ def _tensor_seed(seed: int, name: str) -> int:
 
 
 def random_tensor(name: str, spec: ParamSpec, seed: int, device, dtype: torch.dtype) -> torch.Tensor:
+    shape = spec.concrete_shape()
     if spec.kind == "int":
-        return torch.zeros(spec.shape, dtype=torch.int32, device=device)
+        return torch.zeros(shape, dtype=torch.int32, device=device)
     g = torch.Generator(device=device)
     g.manual_seed(_tensor_seed(seed, name))
     if spec.init == "zeros":
-        return torch.zeros(spec.shape, dtype=dtype, device=device)
+        return torch.zeros(shape, dtype=dtype, device=device)
     n = 1
-    for s in spec.shape:
+    for s in shape:
         n *= s
     # generated in fp32 in slices, so that a large matrix never needs an fp32 copy of itself
     out = torch.empty(n, dtype=dtype, device=device)
@@ -48,7 +49,7 @@ def random_tensor(name: str, spec: ParamSpec, seed: int, device, dtype: torch.dt
         elif spec.init != "normal":
             raise ValueError(f"unknown init '{spec.init}' for {name}")
         out[b:e] = t.to(dtype)
-    return out.reshape(tuple(spec.shape))
+    return out.reshape(shape)
 
 
 def random_tensors(expected: Mapping[str, ParamSpec], seed: int, device="cpu",
