@@ -575,8 +575,39 @@ LODEVIK_SIZES = {
     "small": (_lodevik(1024, 8, 2, 512, 3072, "lalala", 32768), _twin(1024, 8, 2, 3072, 6, 32768)),
     "wide": (_lodevik(4096, 32, 8, 4096, 12288, "lala", 32768), _twin(4096, 32, 8, 12288, 4, 32768)),
 }
+def _sudupel(width, heads, kv_heads, window, ff, experts, top, expert_ff, kinds, vocab):
+    """Layers of kind "p" (attention over every earlier token beside a recurrent gated unit of the model's width in
+    blocks of 256), "w" (windowed attention behind convolutions of 4 taps beside gated linear attention with half the
+    heads, keys of 64 over values of 128, a decay rank of 16) and "l" (linear attention with fixed decays, heads of
+    128); heads of 128; dense feed-forwards of the twin's size and routed ones in turn, whose ``top`` experts do the
+    twin's multiply-adds."""
+    rotary = {"base": 1000000.0, "dims": 128}
+    full = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "rot": dict(rotary, scaling={"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0})}
+    win = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
+           "mask": {"size": window}, "rot": dict(rotary)}
+    mix = {"p": {"left": full, "right": {"width": width, "blocks": width // 256, "conv": 4}, "left_scale": 0.8, "right_scale": 0.9},
+           "w": {"left": win, "right": {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16},
+                 "left_scale": 0.8, "right_scale": 0.5},
+           "l": {"heads": heads, "dim": 128, "vdim": 128,
+                 "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads - 1)) for h in range(heads)]}}
+    kind = {"p": "parallel", "w": "parallel_2", "l": "lightning"}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 3}}}
+    return {"architecture": "Sudupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": width ** 0.5},
+            "logit_softcap": 30.0,
+            "layers": [{"type": kind[k], "mixer": mix[k], "mlp": dense if i % 2 == 0 else moe} for i, k in enumerate(kinds)]}
+
+
+# Sudupel: the three kinds of layer in turn, dense and routed feed-forwards in turn; the twin has the same width, heads,
+# layers, vocabulary and dense feed-forward size (a routed layer's chosen experts do the same multiply-adds)
+SUDUPEL_SIZES = {
+    "lite": (_sudupel(2048, 16, 4, 4096, 6144, 32, 4, 1536, "wplwpp", 32768), _twin(2048, 16, 4, 6144, 6, 32768)),
+    "small": (_sudupel(1024, 8, 2, 512, 3072, 16, 2, 1536, "wplwpp", 32768), _twin(1024, 8, 2, 3072, 6, 32768)),
+    "wide": (_sudupel(4096, 32, 8, 4096, 12288, 16, 2, 6144, "wplp", 32768), _twin(4096, 32, 8, 12288, 4, 32768)),
+}
 DESIGNS = {"nuvilorn": ("Nuvilorn", DESIGN_SIZES), "zekazen": ("Zekazen", ZEKAZEN_SIZES),
-           "lodevik": ("Lodevik", LODEVIK_SIZES)}
+           "lodevik": ("Lodevik", LODEVIK_SIZES), "sudupel": ("Sudupel", SUDUPEL_SIZES)}
 
 
 def design_comparison(args) -> int:

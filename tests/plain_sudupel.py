@@ -4,7 +4,7 @@ tests compare the package's kernels, cache and scheduler with it.
 
 A model is (config, tensors): ``config`` is the design's config.json as a dict, ``tensors`` maps checkpoint names to
 torch tensors.  ``forward(config, tensors, tokens)`` returns (logits [T, vocab], stream after every layer
-[layers, T, width]).
+[layers, T, width], every token's closest routing call).
 """
 from __future__ import annotations
 
@@ -207,44 +207,56 @@ def dense_ff(h, p: str, c: Mapping, tensors) -> torch.Tensor:
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ _w(tensors, p + "down").T
 
 
-def route(z: torch.Tensor, correction: torch.Tensor, top: int, groups: int, keep: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """z [T, E] router logits -> (chosen experts [T, top], their weights).  Scores sigmoid(z); the choice adds the
-    correction; a group's mark is the sum of its two largest choice scores (its one score if it has one expert);
-    experts outside the best ``keep`` groups cannot be chosen; the weights are the scores without the correction."""
+def route(z: torch.Tensor, correction: torch.Tensor, top: int, groups: int, keep: int, tilt: float = 0.0):
+    """z [T, E] router logits -> (chosen experts [T, top], their weights, how close each token's choice was).  Scores
+    sigmoid(z); the choice adds the correction; a group's mark is the sum of its two largest choice scores (its one
+    score if it has one expert); experts outside the best ``keep`` groups cannot be chosen (their choice scores count as
+    minus infinity); the weights are the scores without the correction.  ``tilt`` pushes the choice scores of even
+    experts up and of odd ones down by that much (to find the tokens whose choice hangs on a rounding); the third result
+    is the smallest gap between something chosen and something not (groups' marks, then choice scores)."""
     T, E = z.shape
     s = torch.sigmoid(z)
-    c = s + correction
+    c = s + correction + tilt * (1.0 - 2.0 * (torch.arange(E) % 2)).to(F64)
     per = E // groups
-    cg = c.view(T, groups, per)
-    mark = cg.topk(min(2, per), -1).values.sum(-1)
-    kept = torch.zeros(T, groups, dtype=torch.bool)
-    kept.scatter_(1, mark.topk(keep, -1).indices, True)
-    c = c.masked_fill(~kept[:, :, None].expand(T, groups, per).reshape(T, E), -math.inf)
-    idx = c.topk(top, -1).indices
-    return idx, s.gather(1, idx)
+    margin = torch.full((T,), math.inf, dtype=F64)
+    if groups > 1 and keep < groups:
+        mark = c.view(T, groups, per).topk(min(2, per), -1).values.sum(-1)
+        best = mark.topk(keep + 1, -1)
+        margin = best.values[:, keep - 1] - best.values[:, keep]
+        kept = torch.zeros(T, groups, dtype=torch.bool)
+        kept.scatter_(1, best.indices[:, :keep], True)
+        c = c.masked_fill(~kept[:, :, None].expand(T, groups, per).reshape(T, E), -math.inf)
+    order = c.topk(min(top + 1, E), -1)
+    if top < E:
+        margin = torch.minimum(margin, order.values[:, top - 1] - order.values[:, top])
+    idx = order.indices[:, :top]
+    return idx, s.gather(1, idx), margin
 
 
-def moe_ff(h, p: str, c: Mapping, tensors) -> torch.Tensor:
+def moe_ff(h, p: str, c: Mapping, tensors, tilt: float = 0.0):
     r = c["router"]
     E, top = int(r["experts"]), int(r["top"])
     g = r.get("groups") or {"count": 1, "keep": 1}
-    idx, wgt = route(h @ _w(tensors, p + "router").T, _w(tensors, p + "correction"), top, int(g["count"]), int(g["keep"]))
+    idx, wgt, margin = route(h @ _w(tensors, p + "router").T, _w(tensors, p + "correction"), top, int(g["count"]),
+                             int(g["keep"]), tilt)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for j in range(top):
             e = int(idx[t, j])
             a = silu(_w(tensors, f"{p}e{e}.gate") @ h[t]) * (_w(tensors, f"{p}e{e}.up") @ h[t])
             out[t] += wgt[t, j] * (_w(tensors, f"{p}e{e}.down") @ a)
-    return out
+    return out, margin
 
 
 # ---------------------------------------------------------------------------------------------- the model
-def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: List[int]) -> Tuple[torch.Tensor, torch.Tensor]:
+def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: List[int], tilt: float = 0.0):
+    """-> (logits [T, vocab], the stream after every layer [layers, T, width], every token's closest routing call)."""
     eps = float(config["norm"]["eps"])
     T = len(tokens)
     positions = torch.arange(T)
-    x = _w(tensors, "embed")[torch.tensor(tokens)] * float(config["embedding"]["scale"])
+    x = _w(tensors, "embed")[torch.tensor(tokens)] * float((config.get("embedding") or {}).get("scale", 1.0))
     streams = []
+    margin = torch.full((T,), math.inf, dtype=F64)
     for i, layer in enumerate(config["layers"]):
         p = f"l{i}."
         h = rms_norm(x, _w(tensors, p + "norm1"), eps, True)
@@ -253,7 +265,11 @@ def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: List[i
         ff = layer.get("mlp")
         if ff is not None:
             h = rms_norm(x, _w(tensors, p + "norm2"), eps, True)
-            y = dense_ff(h, p + "mlp.", ff, tensors) if ff["kind"] == "dense" else moe_ff(h, p + "mlp.", ff, tensors)
+            if ff["kind"] == "dense":
+                y = dense_ff(h, p + "mlp.", ff, tensors)
+            else:
+                y, m = moe_ff(h, p + "mlp.", ff, tensors, tilt)
+                margin = torch.minimum(margin, m)
             x = x + rms_norm(y, _w(tensors, p + "norm2b"), eps, True)
         streams.append(x.clone())
     h = rms_norm(x, _w(tensors, "final.norm"), eps, True)
@@ -261,4 +277,4 @@ def forward(config: Mapping, tensors: Mapping[str, torch.Tensor], tokens: List[i
     cap = config.get("logit_softcap")
     if cap:
         logits = float(cap) * torch.tanh(logits / float(cap))
-    return logits, torch.stack(streams)
+    return logits, torch.stack(streams), margin

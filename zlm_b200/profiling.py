@@ -256,6 +256,48 @@ class ProfilingKernels:
         return self._timed(kind, n, 4.0 * T * heads * dim * v_dim, self.k.retention, o, proj, q_off, k_off, v_off, inv_freq,
                            n_rot, decay, state, plan, heads, dim, v_dim, k_scale, pieces, cos_sin)
 
+    # mixers side by side, recurrent mixers, the general q/k/v preparation
+    def attn_prep(self, q_out, proj, conv_w, state, plan, block_table, pool, nq, nkv, dim, vdim, *args, **kw):
+        T, el = proj.shape[0], proj.element_size()
+        n = T * ((nq + nkv) * dim + nkv * vdim) * el + _nbytes(q_out) + T * 2 * nkv * pool.shape[-1] * el
+        return self._timed("conv+qk_norm+rope+cache_write", n, 0, self.k.attn_prep, q_out, proj, conv_w, state, plan,
+                           block_table, pool, nq, nkv, dim, vdim, *args, **kw)
+
+    def norm_gate(self, out, o, g, *args, **kw):
+        return self._timed("heads norm*gate", 2 * _nbytes(out) + _nbytes(o), 0, self.k.norm_gate, out, o, g, *args, **kw)
+
+    def rglru(self, out, proj, *args, **kw):
+        T, W = out.shape
+        blocks = args[-3] if len(args) >= 3 else 1
+        # x and y read, u / gate logits written and read (fp32), the gated output written; the gates' multiply-adds
+        n = 3 * _nbytes(out) + 6 * T * W * 4
+        return self._timed("recurrent gated unit", n, 4.0 * T * W * (W // max(1, int(blocks))), self.k.rglru, out, proj,
+                           *args, **kw)
+
+    def lowrank_decay(self, alpha, proj, lo_off, w2, *args, **kw):
+        return self._timed("decays from a low rank", _nbytes(alpha) + _nbytes(w2), 2.0 * alpha.shape[0] * w2.numel(),
+                           self.k.lowrank_decay, alpha, proj, lo_off, w2, *args, **kw)
+
+    def linear_attention(self, o, proj, q_off, k_off, v_off, alpha, head_decay, state, plan, heads, dim, v_dim, *args, **kw):
+        T, el = proj.shape[0], proj.element_size()
+        n = (T * heads * (2 * dim + v_dim) * el + _nbytes(o) + (0 if alpha is None else _nbytes(alpha))
+             + 2 * plan.R * heads * dim * v_dim * 4)
+        kind = "gated linear attention decode" if plan.is_decode else "gated linear attention prefill"
+        return self._timed(kind, n, 6.0 * T * heads * dim * v_dim, self.k.linear_attention, o, proj, q_off, k_off, v_off,
+                           alpha, head_decay, state, plan, heads, dim, v_dim, *args, **kw)
+
+    def scaled_sum(self, out, a, alpha, b, beta, accumulate=True):
+        return self._timed("two sides summed", 3 * _nbytes(out), 0, self.k.scaled_sum, out, a, alpha, b, beta, accumulate)
+
+    def silu_rows(self, x, cols):
+        return self._timed("silu on q, k, v", 2 * x.shape[0] * cols * x.element_size(), 0, self.k.silu_rows, x, cols)
+
+    def gated_limit(self, out, gu, limit, alpha):
+        return self._timed("gated activation", _nbytes(out) + _nbytes(gu), 0, self.k.gated_limit, out, gu, limit, alpha)
+
+    def softcap_(self, x, cap):
+        return self._timed("logit cap", 2 * _nbytes(x), 0, self.k.softcap_, x, cap)
+
     # latent attention and routed experts
     def latent_prep(self, q, q_rot, dkv, *args, **kw):
         n = _nbytes(q) + _nbytes(q_rot) + 2 * _nbytes(dkv)
