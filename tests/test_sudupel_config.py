@@ -54,7 +54,7 @@ def test_defaults_and_refusals():
     from zlm_b200.registry import config_from_dict
     cfg = config_from_dict(SUDU["B"])
     assert cfg.embedding_scale == 1.0 and cfg.logit_softcap == 0.0
-    assert cfg.layers[0].mlp.groups == 3 and config_from_dict(SUDU["A"]).layers[3].mlp.groups == 1
+    assert cfg.layers[3].mlp.groups == 3 and config_from_dict(SUDU["A"]).layers[3].mlp.groups == 1
     assert config_from_dict(SUDU["A"]).layers[4].mixer.left.rot is None
     bad = [(("layers", 0, "type"), "parallel_3", "type"), (("layers", 0, "mixer", "left", "kv_heads"), 3, "kv_heads"),
            (("layers", 0, "mixer", "right", "blocks"), 5, "blocks"), (("layers", 0, "mlp", "limit"), 0.0, "limit"),

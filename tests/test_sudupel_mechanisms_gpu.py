@@ -133,8 +133,10 @@ def test_recurrent_block_remembers_from_far_back(tmp_path, dtype, sizes):
     assert_rows_close(run_cut(eng, a, [500]), want, dtype, "whole")
     assert_rows_close(run_cut(eng, a, [1, 2, 1, 3, 250, 2, 200], then_single=41), want, dtype, "portions, then single tokens")
     s1, s2 = eng.new_sequence(), eng.new_sequence()
-    got = eng.step([StepEntry(s1, b, [36]), StepEntry(s2, a[:100], [99])]).clone()
-    assert_rows_close(got, torch.stack([P.forward(cfg, ref, b)[0][36], want[99]]), dtype, "side by side")
+    got = eng.step([StepEntry(s1, b, [36]), StepEntry(s2, a[:200], [99, 199])]).clone()          # (pieces, unequal sequences)
+    assert_rows_close(got, torch.stack([P.forward(cfg, ref, b)[0][36], want[99], want[199]]), dtype, "side by side")
+    got = eng.step([StepEntry(s1, a[:5], []), StepEntry(s2, a[200:210], [9])]).clone()
+    assert_rows_close(got, want[209:210], dtype, "going on from the pieces' state")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -153,6 +155,13 @@ def test_gated_linear_attention_remembers_from_far_back(tmp_path, dtype, sizes):
     eng = engine_for(tmp_path, cfg, t, dtype, f"gla{dim}")
     assert_rows_close(run_cut(eng, a, [450]), want, dtype, "whole")
     assert_rows_close(run_cut(eng, a, [17, 2, 300, 1, 90], then_single=40), want, dtype, "portions, then single tokens")
+    # two sequences of unequal length side by side, both in pieces, one of them going on from a state
+    from zlm_b200 import StepEntry
+    (b,) = prompts(cfg["vocab"], [140], seed=14)
+    s1, s2 = eng.new_sequence(), eng.new_sequence()
+    eng.step([StepEntry(s1, a[:70], [])])
+    got = eng.step([StepEntry(s2, b, [139]), StepEntry(s1, a[70:400], [0, 129, 329])]).clone()
+    assert_rows_close(got, torch.stack([P.forward(cfg, ref, b)[0][139], want[70], want[199], want[399]]), dtype, "side by side")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

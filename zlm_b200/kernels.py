@@ -855,15 +855,23 @@ class CudaKernels:
                    c_float(out_scale), self._stream())
 
     # -- recurrent mixers (see csrc/recurrent.cu) ---------------------------------------------------------------
+    # tokens of a sequence from which a step's recurrences run in pieces of 64 tokens side by side
+    RECURRENT_PIECES_FROM = 128
+    RECURRENT_PIECE = 64
+
     def rglru(self, out: torch.Tensor, proj: torch.Tensor, x_off: int, y_off: int, bx: Optional[torch.Tensor],
               by: Optional[torch.Tensor], conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], a_r: torch.Tensor,
               a_i: torch.Tensor, c_r: Optional[torch.Tensor], c_i: Optional[torch.Tensor], lam: torch.Tensor, c_decay: float,
-              state: torch.Tensor, plan, width: int, blocks: int, taps: int, out_scale: float = 1.0) -> None:
+              state: torch.Tensor, plan, width: int, blocks: int, taps: int, out_scale: float = 1.0,
+              gates: Optional[torch.Tensor] = None, pieces: Optional[bool] = None) -> None:
         """The real-gated linear recurrent unit behind its convolution.  ``proj`` [T, >= 2*width] holds the x branch from
         column x_off and the y branch from y_off, without their biases ``bx`` / ``by``; u = conv(x + bx) + conv_b (``conv_w``
         [width, taps]); r, i = sigmoid(A u_b + c) with ``a_r`` / ``a_i`` [blocks, width/blocks, width/blocks] (out, in) on the
         blocks of u; a = exp(-c_decay * r * softplus(lam)); S = a S + sqrt(1 - a^2) i u; out [T, width] = S * gelu_tanh(y + by)
-        * out_scale in the compute dtype.  ``state`` [slots, taps, width] fp32: row 0 is S, the others the newest x + bx."""
+        * out_scale in the compute dtype.  ``state`` [slots, taps, width] fp32: row 0 is S, the others the newest x + bx.
+        ``gates`` [blocks, 2*width/blocks, width/blocks] (the rows of a_r[b], then of a_i[b]): bfloat16 steps of more than 16
+        tokens compute the gates' logits block by block as products of the library with fp32 sums and fp32 output.  Long
+        prompts run in pieces side by side (``pieces`` forces or forbids that)."""
         T = proj.shape[0]
         W = width
         dt = proj.dtype
@@ -876,14 +884,33 @@ class CudaKernels:
         for v in (bx, by, conv_b, c_r, c_i, lam):
             assert v is None or (v.numel() == W and v.is_contiguous() and v.dtype == dt)
         u = plan.scratch("rglru.u", (T, W), torch.float32)
-        zr = plan.scratch("rglru.zr", (T, W), torch.float32)
-        zi = plan.scratch("rglru.zi", (T, W), torch.float32)
-        self._call("zlm_rglru", self._p(out), c_int(out.stride(0)), self._p(u), self._p(zr), self._p(zi), self._p(proj),
-                   c_int(proj.stride(0)), c_int(x_off), c_int(y_off), self._p(bx), self._p(by), self._p(conv_w), self._p(conv_b),
-                   self._p(a_r), self._p(a_i), self._p(c_r), self._p(c_i), self._p(lam), c_float(c_decay), self._p(state),
-                   c_int(_dt(proj)), self._p(plan.token_pos), self._p(plan.token_slot), self._p(plan.token_seq),
-                   self._p(plan.seq_start), self._p(plan.cu_seqlens), self._p(plan.seq_slot), c_int(T), c_int(plan.R), c_int(W),
-                   c_int(blocks), c_int(taps), c_float(out_scale), self._stream())
+        z = plan.scratch("rglru.z", (T, blocks, 2 * bs), torch.float32)
+        max_new = int(getattr(plan, "max_new", 0) or 0)
+        if pieces is None:
+            pieces = max_new >= self.RECURRENT_PIECES_FROM
+        part = None
+        if pieces:
+            maxp = (max_new + self.RECURRENT_PIECE - 1) // self.RECURRENT_PIECE
+            part = plan.scratch("rglru.pieces", (2 * plan.R * maxp * W,), torch.float32)
+        by_products = (gates is not None and dt == torch.bfloat16 and T > 16 and bs % 8 == 0 and W % 8 == 0)
+        u16 = plan.scratch("rglru.u16", (T, W), dt) if by_products else None
+
+        def call(phase: int) -> None:
+            self._call("zlm_rglru", self._p(out), c_int(out.stride(0)), self._p(u), self._p(u16), self._p(z), self._p(proj),
+                       c_int(proj.stride(0)), c_int(x_off), c_int(y_off), self._p(bx), self._p(by), self._p(conv_w),
+                       self._p(conv_b), self._p(a_r), self._p(a_i), self._p(c_r), self._p(c_i), self._p(lam), c_float(c_decay),
+                       self._p(state), c_int(_dt(proj)), self._p(plan.token_pos), self._p(plan.token_slot),
+                       self._p(plan.token_seq), self._p(plan.seq_start), self._p(plan.cu_seqlens), self._p(plan.seq_slot),
+                       c_int(T), c_int(plan.R), c_int(W), c_int(blocks), c_int(taps), c_float(out_scale), c_int(max_new),
+                       self._p(part), c_int(phase), self._stream())
+        if not by_products:
+            call(0)
+            return
+        assert gates.shape == (blocks, 2 * bs, bs) and gates.is_contiguous() and gates.dtype == dt
+        call(1)
+        for b in range(blocks):
+            self.linear(z[:, b], u16[:, b * bs:(b + 1) * bs], gates[b])
+        call(2)
 
     def lowrank_decay(self, alpha: torch.Tensor, proj: torch.Tensor, lo_off: int, w2: torch.Tensor, b: Optional[torch.Tensor],
                       tau: float) -> None:
@@ -897,10 +924,12 @@ class CudaKernels:
 
     def linear_attention(self, o: torch.Tensor, proj: torch.Tensor, q_off: int, k_off: int, v_off: int,
                          alpha: Optional[torch.Tensor], head_decay: Optional[torch.Tensor], state: torch.Tensor, plan,
-                         heads: int, dim: int, v_dim: int, q_scale: float = 1.0) -> None:
+                         heads: int, dim: int, v_dim: int, q_scale: float = 1.0, pieces: Optional[bool] = None) -> None:
         """o [T, heads*v_dim] fp32 = S_t^T q_t with S_t = diag(alpha_t) S_(t-1) + k_t v_t^T per head; q (times ``q_scale``),
         k, v are columns of ``proj`` from q_off, k_off, v_off on; ``alpha`` [T, heads*dim] fp32 gives a decay per token and
-        key channel, or ``head_decay`` [heads] fp32 one per head; ``state`` [slots, heads, dim, v_dim] fp32."""
+        key channel, or ``head_decay`` [heads] fp32 one per head; ``state`` [slots, heads, dim, v_dim] fp32.  Long prompts
+        run in pieces of 64 tokens side by side: every piece from a zero state, the pieces' states chained, and a second
+        pass that adds what the state before a piece gives its tokens (``pieces`` forces or forbids that)."""
         T = proj.shape[0]
         assert o.shape == (T, heads * v_dim) and o.dtype == torch.float32 and o.is_contiguous() and proj.stride(1) == 1
         assert state.dtype == torch.float32 and tuple(state.shape[1:]) == (heads, dim, v_dim) and state.is_contiguous()
@@ -908,10 +937,17 @@ class CudaKernels:
             assert alpha.shape == (T, heads * dim) and alpha.dtype == torch.float32 and alpha.is_contiguous()
         else:
             assert head_decay is not None and head_decay.dtype == torch.float32 and head_decay.numel() == heads
+        max_new = int(getattr(plan, "max_new", 0) or 0)
+        if pieces is None:
+            pieces = max_new >= self.RECURRENT_PIECES_FROM
+        part = None
+        if pieces:
+            maxp = (max_new + self.RECURRENT_PIECE - 1) // self.RECURRENT_PIECE
+            part = plan.scratch("linear_attention.pieces", (plan.R * maxp * heads * dim * (v_dim + 1),), torch.float32)
         self._call("zlm_linear_attention", self._p(o), self._p(proj), c_int(proj.stride(0)), c_int(q_off), c_int(k_off),
                    c_int(v_off), self._p(alpha), self._p(head_decay if alpha is None else None), self._p(state), c_int(_dt(proj)),
                    self._p(plan.seq_slot), self._p(plan.cu_seqlens), c_int(T), c_int(plan.R), c_int(heads), c_int(dim),
-                   c_int(v_dim), c_float(q_scale), self._stream())
+                   c_int(v_dim), c_float(q_scale), c_int(max_new), self._p(part), self._stream())
 
     def scaled_sum(self, out: torch.Tensor, a: torch.Tensor, alpha: float, b: torch.Tensor, beta: float,
                    accumulate: bool = True) -> None:

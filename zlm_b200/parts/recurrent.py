@@ -62,6 +62,10 @@ class RecurrentGatedUnit(Mixer):
                       ("y_proj.bias", "x_proj.bias", "conv.weight", "conv.bias", "a_gate.weight", "a_gate.bias",
                        "i_gate.weight", "i_gate.bias", "lam")}
         self.w_o = params.pop("o_proj.weight")
+        # the two gates' matrices block by block, [A_r[b] ; A_i[b]]: what a many-token bfloat16 step multiplies on the
+        # tensor cores
+        self.w_gates = (torch.cat([self.small["a_gate.weight"], self.small["i_gate.weight"]], dim=1).contiguous()
+                        if dt == torch.bfloat16 else None)
         self.check_products(in_proj=self.w_in, o_proj=self.w_o)
 
     def tensors(self) -> Dict[str, torch.Tensor]:
@@ -76,7 +80,7 @@ class RecurrentGatedUnit(Mixer):
         gated = rt.ws.get("rglru.gated", (T, self.W), rt.dtype)
         k.rglru(gated, proj, self.W, 0, p["x_proj.bias"], p["y_proj.bias"], p["conv.weight"], p["conv.bias"],
                 p["a_gate.weight"], p["i_gate.weight"], p["a_gate.bias"], p["i_gate.bias"], p["lam"], self.c_decay, io.state,
-                ctx, self.W, self.B, self.taps, self.out_scale)
+                ctx, self.W, self.B, self.taps, self.out_scale, gates=self.w_gates)
         k.linear(residual, gated, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next
 
 

@@ -268,7 +268,7 @@ class ProfilingKernels:
 
     def rglru(self, out, proj, *args, **kw):
         T, W = out.shape
-        blocks = args[-3] if len(args) >= 3 else 1
+        blocks = args[15] if len(args) > 15 else 1
         # x and y read, u / gate logits written and read (fp32), the gated output written; the gates' multiply-adds
         n = 3 * _nbytes(out) + 6 * T * W * 4
         return self._timed("recurrent gated unit", n, 4.0 * T * W * (W // max(1, int(blocks))), self.k.rglru, out, proj,
