@@ -196,14 +196,15 @@ class Oracle:
         if dtype != "float32":
             # positions where the design itself multiplies a rounding tenfold (a recurrence's output at a sequence's
             # first positions is one or two terms, (q.k) v, whose sign decides everything once the heads are divided
-            # by their root mean square): one more run on embeddings moved by a bfloat16 rounding (a relative 2^-8);
+            # by their root mean square): three more runs on embeddings moved by a bfloat16 rounding or two (a relative 2^-7);
             # where that moves the logits by 4 % and more, no bfloat16 run can be held to the oracle
-            g = torch.Generator().manual_seed(77)
-            moved = dict(tensors)
-            moved["embed"] = tensors["embed"] * (1.0 + 2.0 ** -8 * (2.0 * torch.rand(tensors["embed"].shape, generator=g,
-                                                                                      dtype=torch.float64) - 1.0))
-            other = P.forward(cfg, moved, ids)[0]
-            self.safe &= (other - logits).norm(dim=-1) <= 0.04 * logits.norm(dim=-1)
+            for seed in (77, 78, 79):
+                g = torch.Generator().manual_seed(seed)
+                moved = dict(tensors)
+                moved["embed"] = tensors["embed"] * (1.0 + 2.0 ** -7 * (2.0 * torch.rand(tensors["embed"].shape, generator=g,
+                                                                                          dtype=torch.float64) - 1.0))
+                other = P.forward(cfg, moved, ids)[0]
+                self.safe &= (other - logits).norm(dim=-1) <= 0.04 * logits.norm(dim=-1)
 
     def check(self, got: torch.Tensor, places, dtype: str, what: str = "") -> None:
         places = list(places)

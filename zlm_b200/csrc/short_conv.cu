@@ -354,7 +354,8 @@ attn_prep_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __restrict_
     int page = 0;
     if (ZLM_CHK(block_table + (size_t)slot * table_stride + pos / ZLM_PAGE, 4))
         page = block_table[(size_t)slot * table_stride + pos / ZLM_PAGE];
-    for (int x = tid; x < (nq + 2 * nkv) * hdp; x += AP_THREADS) {
+    // (steps of few tokens run several blocks a token: each repeats the sums above and writes its share)
+    for (int x = blockIdx.y * AP_THREADS + tid; x < (nq + 2 * nkv) * hdp; x += AP_THREADS * gridDim.y) {
         const int unit = x / hdp, e = x - unit * hdp;
         float o = 0.f;
         if (unit < nq + nkv) {
@@ -397,7 +398,11 @@ static void launch_attn_prep(void* q_out, int q_out_stride, const void* proj, in
                              VecW k_w, float eps, const float* inv_freq, int n_rot, float rot_scale, cudaStream_t st) {
     const int C = (nq + nkv) * dim + nkv * vdim;
     const size_t smem = (size_t)(C + nq + nkv + 32) * sizeof(float);
-    zlm_launch(attn_prep_kernel<TA>, dim3(T), dim3(AP_THREADS), smem, st, (TA*)q_out, q_out_stride, (const TA*)proj,
+    // blocks a token: one where the tokens alone fill the device, else as many as give it two rounds of work
+    int share = 1;
+    const int outputs = (nq + 2 * nkv) * hdp;
+    while (share < 16 && (long long)T * share < 296 && outputs > share * AP_THREADS * 2) share *= 2;
+    zlm_launch(attn_prep_kernel<TA>, dim3(T, share), dim3(AP_THREADS), smem, st, (TA*)q_out, q_out_stride, (const TA*)proj,
                proj_stride, (const TA*)conv_w, (const TA*)state, token_pos, token_slot, token_seq, seq_start, cu_seqlens,
                block_table, table_stride, (TA*)pool, nq, nkv, dim, vdim, hdp, taps, norm_mode, q_w, k_w, eps, inv_freq, n_rot,
                rot_scale);
