@@ -578,24 +578,24 @@ LODEVIK_SIZES = {
 def _sudupel(width, heads, kv_heads, window, ff, experts, top, expert_ff, kinds, vocab):
     """Layers of kind "p" (attention over every earlier token beside a recurrent gated unit of the model's width in
     blocks of 256), "w" (windowed attention behind convolutions of 4 taps beside gated linear attention with half the
-    heads, keys of 64 over values of 128, a decay rank of 16) and "l" (linear attention with fixed decays, heads of
+    heads, keys of 64 over values of 128, a decay rank of 32) and "l" (linear attention with fixed decays, heads of
     128); heads of 128; dense feed-forwards of the twin's size and routed ones in turn, whose ``top`` experts do the
     twin's multiply-adds."""
-    rotary = {"base": 1000000.0, "dims": 128}
+    rotary = {"base": 500000.0, "dims": 128}
     full = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-            "rot": dict(rotary, scaling={"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0})}
+            "rot": dict(rotary, scaling={"factor": 4.0, "original": 4096, "fast": 16.0, "slow": 2.0})}
     win = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
            "mask": {"size": window}, "rot": dict(rotary)}
-    mix = {"p": {"left": full, "right": {"width": width, "blocks": width // 256, "conv": 4}, "left_scale": 0.8, "right_scale": 0.9},
-           "w": {"left": win, "right": {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16},
-                 "left_scale": 0.8, "right_scale": 0.5},
+    mix = {"p": {"left": full, "right": {"width": width, "blocks": width // 256, "conv": 4}, "left_scale": 0.7, "right_scale": 1.0},
+           "w": {"left": win, "right": {"heads": heads // 2, "dim": 64, "vdim": 128, "tau": 8.0, "rank": 32},
+                 "left_scale": 0.7, "right_scale": 0.6},
            "l": {"heads": heads, "dim": 128, "vdim": 128,
                  "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads - 1)) for h in range(heads)]}}
     kind = {"p": "parallel", "w": "parallel_2", "l": "lightning"}
     dense = {"kind": "dense", "ff": ff, "limit": 7.0}
-    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 3}}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": 8, "keep": 4}}}
     return {"architecture": "Sudupel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": width ** 0.5},
-            "logit_softcap": 30.0,
+            "logit_softcap": 50.0,
             "layers": [{"type": kind[k], "mixer": mix[k], "mlp": dense if i % 2 == 0 else moe} for i, k in enumerate(kinds)]}
 
 

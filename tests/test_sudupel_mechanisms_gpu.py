@@ -359,3 +359,29 @@ def test_small_kernels(dtype):
             gz = gate[:, :H * V].double().cpu()
             ref = ref * (torch.sigmoid(gz) if act_name == "sigmoid" else P.silu(gz) if act_name == "silu" else 1.0) * 0.5
             assert torch.allclose(res.double().cpu(), ref, atol=1e-5 if dtype == "float32" else 3e-2), (group, act_name)
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 16, 17, 40, 64, 100, 128, 300, 500])
+@pytest.mark.parametrize("I, K_", [(64, 40), (200, 1000), (1536, 512)])
+def test_clamped_gate_in_the_epilogue_of_the_products(T, I, K_):
+    """``linear_swiglu(act="swish_limit")`` on the streaming product, the tcgen05 forms and the mma.sync fallback against
+    the plain clamped halves, with two different pairs of constants one after the other (each product gets its own), and
+    the silu form of the same call after it still is silu."""
+    from zlm_b200.kernels import get_kernels, interleave_gate_up
+    k = get_kernels()
+    g = torch.Generator().manual_seed(71)
+    x = (1.5 * torch.randn(T, K_, generator=g)).to(torch.bfloat16)
+    gate = (torch.randn(I, K_, generator=g) * K_ ** -0.5).to(torch.bfloat16)
+    up = (torch.randn(I, K_, generator=g) * K_ ** -0.5).to(torch.bfloat16)
+    w = interleave_gate_up(gate.cuda(), up.cuda())
+    g64, u64 = x.double() @ gate.double().T, x.double() @ up.double().T
+    for impl in (None, "mma", "gemv" if T <= 16 else None):
+        for limit, alpha in ((0.8, 1.702), (2.5, 1.0)):
+            out = torch.zeros(T, I, dtype=torch.bfloat16, device="cuda")
+            k.linear_swiglu(out, x.cuda(), w, impl=impl, act="swish_limit", limit=limit, alpha=alpha)
+            gg, uu = g64.clamp(max=limit), u64.clamp(-limit, limit)
+            want = gg * torch.sigmoid(alpha * gg) * (uu + 1.0)
+            assert torch.allclose(out.double().cpu(), want, atol=2e-2, rtol=2e-2), f"impl={impl} limit={limit}"
+        k.linear_swiglu(out, x.cuda(), w, impl=impl)
+        assert torch.allclose(out.double().cpu(), g64 * torch.sigmoid(g64) * u64, atol=2e-2, rtol=2e-2), f"silu impl={impl}"
+    assert k.gemm_tc_status() == 0

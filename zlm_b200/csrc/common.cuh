@@ -262,10 +262,30 @@ static inline void zlm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);     // errors surface in zlm_check_launch
 }
 
-// The products' gated modes: 3, silu(gate) * up, and 7, gelu_tanh(gate) * up, with
-// gelu_tanh(z) = 0.5 z (1 + tanh(c (z + 0.044715 z^3))) = z / (1 + e^{-2 c (z + 0.044715 z^3)}), c = sqrt(2 / pi)
-#define ZLM_GATED(M) ((M) == 3 || (M) == 7)
+// The products' gated modes: 3, silu(gate) * up; 7, gelu_tanh(gate) * up, with
+// gelu_tanh(z) = 0.5 z (1 + tanh(c (z + 0.044715 z^3))) = z / (1 + e^{-2 c (z + 0.044715 z^3)}), c = sqrt(2 / pi); and
+// 8, g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit).  Mode 8's two constants live in
+// a device variable of the translation unit that runs the product: a one-thread kernel in the product's stream sets
+// them before it (a kernel with its two numbers as arguments, so that a captured step replays them), after the kernels
+// before it have finished (griddepcontrol.wait), and every product waits for the kernel before it ahead of its epilogue.
+#define ZLM_GATED(M) ((M) == 3 || (M) == 7 || (M) == 8)
+static __device__ float2 g_zlm_gate = {0.f, 1.f};
+static __global__ void zlm_gate_set_kernel(float limit, float alpha) {
+    pdl_wait();
+    g_zlm_gate = make_float2(limit, alpha);
+}
 template <int MODE> __device__ __forceinline__ float gated_mul(float g, float u) {
     if (MODE == 7) return (g / (1.0f + expf(-1.5957691216057308f * (g + 0.044715f * g * g * g)))) * u;
+    if (MODE == 8) {
+        const float2 p = g_zlm_gate;
+        const float gg = fminf(g, p.x), uu = fminf(fmaxf(u, -p.x), p.x);
+        return (gg / (1.0f + expf(-p.y * gg))) * (uu + 1.0f);
+    }
     return (g / (1.0f + expf(-g))) * u;
 }
+// a translation unit with gated products ends with ZLM_GATE_SETTER(name) as well
+#define ZLM_GATE_SETTER(name)                                                              \
+    extern "C" int zlm_set_gate_##name(float limit, float alpha, cudaStream_t st) {       \
+        zlm_launch(zlm_gate_set_kernel, dim3(1), dim3(1), 0, st, limit, alpha);            \
+        return zlm_check_launch("set_gate");                                               \
+    }

@@ -192,7 +192,8 @@ static int launch_mma(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, i
     else if (mode == 1) ZLM_LAUNCH_MODE(1)
     else if (mode == 2) ZLM_LAUNCH_MODE(2)
     else if (mode == 3) ZLM_LAUNCH_MODE(3)
-    else ZLM_LAUNCH_MODE(7)
+    else if (mode == 7) ZLM_LAUNCH_MODE(7)
+    else ZLM_LAUNCH_MODE(8)
 #undef ZLM_LAUNCH_MODE
     return zlm_check_launch("gemm_bf16_mma");
 }
@@ -206,7 +207,7 @@ extern "C" int zlm_gemm_bf16_mma(void* Y, const void* X, const void* W, int T, i
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemm_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_bf16: operands must be 16-byte aligned");
-    ZLM_REQUIRE((mode >= 0 && mode <= 3) || mode == 7, "gemm_bf16: mode %d", mode);
+    ZLM_REQUIRE((mode >= 0 && mode <= 3) || mode == 7 || mode == 8, "gemm_bf16: mode %d", mode);
     ZLM_REQUIRE(!ZLM_GATED(mode) || N % 16 == 0, "gemm_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
@@ -217,3 +218,4 @@ extern "C" int zlm_gemm_bf16_mma(void* Y, const void* X, const void* W, int T, i
 }
 
 ZLM_TRANSLATION_UNIT(gemm_bf16_mma)
+ZLM_GATE_SETTER(gemm_bf16_mma)

@@ -1045,7 +1045,8 @@ static int launch_reduce(void* Y, const float* scratch, int T, int N, int ldy, i
     else if (mode == 1) zlm_launch(gemm_tc_reduce_kernel<1>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
     else if (mode == 2) zlm_launch(gemm_tc_reduce_kernel<2>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
     else if (mode == 3) zlm_launch(gemm_tc_reduce_kernel<3>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
-    else zlm_launch(gemm_tc_reduce_kernel<7>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    else if (mode == 7) zlm_launch(gemm_tc_reduce_kernel<7>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    else zlm_launch(gemm_tc_reduce_kernel<8>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
     return zlm_check_launch("gemm_tc_reduce");
 }
 
@@ -1146,6 +1147,7 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
     else if (kmode == 2) ZLM_TC_LAUNCH(2)
     else if (kmode == 3) ZLM_TC_LAUNCH(3)
     else if (kmode == 7) ZLM_TC_LAUNCH(7)
+    else if (kmode == 8) ZLM_TC_LAUNCH(8)
     else ZLM_TC_LAUNCH(4)
 #undef ZLM_TC_LAUNCH
     rc = zlm_check_launch("gemm_tc");
@@ -1193,7 +1195,8 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
     else if (mode == 1) ZLM_TCP_LAUNCH(1)
     else if (mode == 2) ZLM_TCP_LAUNCH(2)
     else if (mode == 3) ZLM_TCP_LAUNCH(3)
-    else ZLM_TCP_LAUNCH(7)
+    else if (mode == 7) ZLM_TCP_LAUNCH(7)
+    else ZLM_TCP_LAUNCH(8)
 #undef ZLM_TCP_LAUNCH
     return zlm_check_launch("gemm_tc_persistent");
 }
@@ -1210,7 +1213,7 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
     // the results go through the copy engine where the output's rows can be described to it
     // (16-byte aligned rows); else the threads store row by row
     const int ybytes = (mode == 0 || ZLM_GATED(mode)) ? 2 : 4;
-    const int y_tma = ((mode >= 0 && mode <= 3) || mode == 7) && ((size_t)ldy * ybytes) % 16 == 0 && (uintptr_t)Y % 16 == 0 &&
+    const int y_tma = ((mode >= 0 && mode <= 3) || mode == 7 || mode == 8) && ((size_t)ldy * ybytes) % 16 == 0 && (uintptr_t)Y % 16 == 0 &&
                       (!ZLM_GATED(mode) || N % 2 == 0);
     CUtensorMap my = mx;
     if (y_tma) {
@@ -1241,7 +1244,8 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
         if constexpr (BN == 256 || BN == 128) ZLM_TCQ_LAUNCH(5)
     }
     else if (mode == 3) ZLM_TCQ_LAUNCH(3)
-    else ZLM_TCQ_LAUNCH(7)
+    else if (mode == 7) ZLM_TCQ_LAUNCH(7)
+    else ZLM_TCQ_LAUNCH(8)
 #undef ZLM_TCQ_LAUNCH
     return zlm_check_launch("gemm_tc_pair");
 }
@@ -1309,7 +1313,8 @@ static int launch_tc_few(void* Y, const void* X, const void* W, int T, int N, in
     else if (mode == 1) ZLM_TCF_LAUNCH(1)
     else if (mode == 2) ZLM_TCF_LAUNCH(2)
     else if (mode == 3) ZLM_TCF_LAUNCH(3)
-    else ZLM_TCF_LAUNCH(7)
+    else if (mode == 7) ZLM_TCF_LAUNCH(7)
+    else ZLM_TCF_LAUNCH(8)
 #undef ZLM_TCF_LAUNCH
     rc = zlm_check_launch("gemm_tc_few");
     if (rc || plan.ks <= 1) return rc;
@@ -1407,7 +1412,7 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
     if (T == 0 || N == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_gemm_tc_supported(T, N, K, ldx), "gemm_tc: shape T=%d N=%d K=%d (row stride %d) is not taken", T, N, K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
-    ZLM_REQUIRE((mode >= 0 && mode <= 3) || mode == 7, "gemm_tc: mode %d", mode);
+    ZLM_REQUIRE((mode >= 0 && mode <= 3) || mode == 7 || mode == 8, "gemm_tc: mode %d", mode);
     ZLM_REQUIRE(!ZLM_GATED(mode) || N % 16 == 0, "gemm_tc: the fused gate/up product needs N=%d to be a multiple of 16", N);
     const int ks = zlm_gemm_tc_ksplit(T, N, K);
     ZLM_REQUIRE(ks == 1 || scratch, "gemm_tc: scratch for %d shares of K is missing", ks);
@@ -1605,3 +1610,4 @@ extern "C" int zlm_test_bounded_wait(const void* src, int* out, unsigned long lo
 }
 
 ZLM_TRANSLATION_UNIT(gemm_tcgen05)
+ZLM_GATE_SETTER(gemm_tcgen05)

@@ -318,6 +318,7 @@ static int launch_gemv_w(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W
     else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     else if (mode == 3) zlm_launch(gemv_bf16_kernel<NT, 3, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     else if (mode == 7) zlm_launch(gemv_bf16_kernel<NT, 7, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
+    else if (mode == 8) zlm_launch(gemv_bf16_kernel<NT, 8, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     else zlm_launch(gemv_bf16_kernel<NT, 4, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     return zlm_check_launch("gemv_bf16");
 }
@@ -352,7 +353,7 @@ static int gemv_entry(void* Y, const void* X, const void* W, int T, int N, int K
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemv_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemv_bf16: operands must be 16-byte aligned");
-    ZLM_REQUIRE((mode >= 0 && mode <= 4) || mode == 7, "gemv_bf16: mode %d", mode);
+    ZLM_REQUIRE((mode >= 0 && mode <= 4) || mode == 7 || mode == 8, "gemv_bf16: mode %d", mode);
     ZLM_REQUIRE(!ZLM_GATED(mode) || N % 16 == 0, "gemv_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
     ZLM_REQUIRE(mode != 4 || (nm.weight.p && nm.next && nm.squares), "gemv_bf16: the following norm's weight and outputs are missing");
     ZLM_REQUIRE(!nm.in_squares || nm.in_blocks > 0, "gemv_bf16: sums of squares of %d blocks", nm.in_blocks);
@@ -393,3 +394,4 @@ extern "C" int zlm_gemv_bf16_norms(void* Y, const void* X, const void* W, int T,
 }
 
 ZLM_TRANSLATION_UNIT(gemv_bf16)
+ZLM_GATE_SETTER(gemv_bf16)

@@ -188,6 +188,7 @@ __device__ __forceinline__ void rglru_keep_inputs(float* sp, const TA* proj, int
 // Short steps: a thread owns one channel of one sequence and walks the step's tokens (eight tokens' loads in flight),
 // then leaves the state: row 0 the recurrence's S, rows 1 .. taps-1 the newest x + bx.
 #define RS_AHEAD 8
+#define PIECE_AHEAD 16          // the pieces' walks: a piece is two such rounds
 template <typename TA>
 __global__ void __launch_bounds__(128)
 rglru_scan_kernel(TA* __restrict__ out, int out_stride, const float* __restrict__ u, const float* __restrict__ z,
@@ -251,10 +252,10 @@ rglru_piece_ab_kernel(float* __restrict__ z, const float* __restrict__ u, const 
     const float rb = cr ? vr[c] : 0.f, ib = ci ? vi[c] : 0.f;
     const size_t zc = (size_t)(c / bs) * 2 * bs + (c % bs);
     float A = 1.f, B = 0.f;
-    for (int s0 = lo; s0 < hi; s0 += RS_AHEAD) {
-        float fu[RS_AHEAD], fr[RS_AHEAD], fi[RS_AHEAD];
+    for (int s0 = lo; s0 < hi; s0 += PIECE_AHEAD) {
+        float fu[PIECE_AHEAD], fr[PIECE_AHEAD], fi[PIECE_AHEAD];
 #pragma unroll
-        for (int j = 0; j < RS_AHEAD; ++j) {
+        for (int j = 0; j < PIECE_AHEAD; ++j) {
             const size_t row = (size_t)(row0 + s0 + j);
             const bool ok = s0 + j < hi && ZLM_CHK(u + row * W + c, 4) && ZLM_CHK(z + row * 2 * W + zc, 4) && ZLM_CHK(z + row * 2 * W + zc + bs, 4);
             fu[j] = ok ? u[row * W + c] : 0.f;
@@ -262,7 +263,7 @@ rglru_piece_ab_kernel(float* __restrict__ z, const float* __restrict__ u, const 
             fi[j] = ok ? z[row * 2 * W + zc + bs] : 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < RS_AHEAD; ++j) {
+        for (int j = 0; j < PIECE_AHEAD; ++j) {
             if (s0 + j >= hi) break;
             float a, b;
             rglru_ab(fr[j] + rb, fi[j] + ib, fu[j], sl, a, b);
@@ -331,10 +332,10 @@ rglru_piece_out_kernel(TA* __restrict__ out, int out_stride, const float* __rest
     float S = ZLM_CHK(S0 + at, 4) ? S0[at] : 0.f;
     const float yb = by ? to_f32(by[c]) : 0.f;
     const size_t zc = (size_t)(c / bs) * 2 * bs + (c % bs);
-    for (int s0 = lo; s0 < hi; s0 += RS_AHEAD) {
-        float fa[RS_AHEAD], fb[RS_AHEAD], fy[RS_AHEAD];
+    for (int s0 = lo; s0 < hi; s0 += PIECE_AHEAD) {
+        float fa[PIECE_AHEAD], fb[PIECE_AHEAD], fy[PIECE_AHEAD];
 #pragma unroll
-        for (int j = 0; j < RS_AHEAD; ++j) {
+        for (int j = 0; j < PIECE_AHEAD; ++j) {
             const size_t row = (size_t)(row0 + s0 + j);
             const bool ok = s0 + j < hi && ZLM_CHK(z + row * 2 * W + zc, 4) && ZLM_CHK(z + row * 2 * W + zc + bs, 4) &&
                             ZLM_CHK(proj + row * proj_stride + y_off + c, sizeof(TA));
@@ -343,7 +344,7 @@ rglru_piece_out_kernel(TA* __restrict__ out, int out_stride, const float* __rest
             fy[j] = ok ? to_f32(proj[row * proj_stride + y_off + c]) : 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < RS_AHEAD; ++j) {
+        for (int j = 0; j < PIECE_AHEAD; ++j) {
             if (s0 + j >= hi) break;
             S = fmaf(fa[j], S, fb[j]);
             TA* dst = out + (size_t)(row0 + s0 + j) * out_stride + c;
@@ -352,7 +353,7 @@ rglru_piece_out_kernel(TA* __restrict__ out, int out_stride, const float* __rest
     }
 }
 
-#define RGLRU_PIECE 64
+#define RGLRU_PIECE 32
 template <typename TA>
 static void launch_rglru(void* out, int out_stride, float* u, void* u16, float* z, int gates_done, const void* proj,
                          int proj_stride, int x_off, int y_off, const void* bx, const void* by, const void* conv_w,
@@ -400,8 +401,8 @@ static void launch_rglru(void* out, int out_stride, float* u, void* u16, float* 
 // S * gelu_tanh(y) * out_scale in the element type.
 // phase 0: everything; 1: the convolution only (the caller then computes z = u16_b [A_r[b] ; A_i[b]]^T block by block
 // with a product of its own); 2: what follows the gates' logits (gates_done 1: z holds them).
-// pieces: null (a thread walks a sequence's tokens), or 2 * R * ceil(max_new / 64) * W floats: sequences run in pieces of
-// 64 tokens side by side.
+// pieces: null (a thread walks a sequence's tokens), or 2 * R * ceil(max_new / 32) * W floats: sequences run in pieces of
+// 32 tokens side by side.
 extern "C" int zlm_rglru(void* out, int out_stride, float* u, void* u16, float* z, const void* proj, int proj_stride, int x_off,
                          int y_off, const void* bx, const void* by, const void* conv_w, const void* cb, const void* Ar,
                          const void* Ai, const void* cr, const void* ci, const void* lam, float c_decay, float* state, int dtype,
@@ -537,23 +538,24 @@ linear_attention_kernel(float* __restrict__ o, const TA* __restrict__ proj, int 
             for (int j = 0; j < m; ++j) pd *= sa[j][tid];
         for (int j = 0; j < m; ++j) {
             const float vv = MODE == 2 ? 0.f : sv[j][tid];
-            float acc = 0.f;
+            float c0 = 0.f, c1 = 0.f, c2 = 0.f, c3 = 0.f;         // four sums side by side (always added in this order)
 #pragma unroll
             for (int d = 0; d < DR; d += 4) {
                 const float4 a4 = *(const float4*)&sa[j][d], q4 = *(const float4*)&sq[j][d];
                 if (MODE == 2) {
-                    S[d] *= a4.x;     acc = fmaf(S[d], q4.x, acc);
-                    S[d + 1] *= a4.y; acc = fmaf(S[d + 1], q4.y, acc);
-                    S[d + 2] *= a4.z; acc = fmaf(S[d + 2], q4.z, acc);
-                    S[d + 3] *= a4.w; acc = fmaf(S[d + 3], q4.w, acc);
+                    S[d] *= a4.x;     c0 = fmaf(S[d], q4.x, c0);
+                    S[d + 1] *= a4.y; c1 = fmaf(S[d + 1], q4.y, c1);
+                    S[d + 2] *= a4.z; c2 = fmaf(S[d + 2], q4.z, c2);
+                    S[d + 3] *= a4.w; c3 = fmaf(S[d + 3], q4.w, c3);
                 } else {
                     const float4 k4 = *(const float4*)&sk[j][d];
-                    S[d] = fmaf(a4.x, S[d], k4.x * vv);         acc = fmaf(S[d], q4.x, acc);
-                    S[d + 1] = fmaf(a4.y, S[d + 1], k4.y * vv); acc = fmaf(S[d + 1], q4.y, acc);
-                    S[d + 2] = fmaf(a4.z, S[d + 2], k4.z * vv); acc = fmaf(S[d + 2], q4.z, acc);
-                    S[d + 3] = fmaf(a4.w, S[d + 3], k4.w * vv); acc = fmaf(S[d + 3], q4.w, acc);
+                    S[d] = fmaf(a4.x, S[d], k4.x * vv);         c0 = fmaf(S[d], q4.x, c0);
+                    S[d + 1] = fmaf(a4.y, S[d + 1], k4.y * vv); c1 = fmaf(S[d + 1], q4.y, c1);
+                    S[d + 2] = fmaf(a4.z, S[d + 2], k4.z * vv); c2 = fmaf(S[d + 2], q4.z, c2);
+                    S[d + 3] = fmaf(a4.w, S[d + 3], k4.w * vv); c3 = fmaf(S[d + 3], q4.w, c3);
                 }
             }
+            const float acc = (c0 + c1) + (c2 + c3);
             float* op = o + ((size_t)(row0 + s0 + j) * H + h) * V + v;
             if (v < V && ZLM_CHK(op, 4)) *op = MODE == 2 ? *op + acc : acc;
         }
@@ -606,10 +608,10 @@ linear_attention_chain_kernel(float* __restrict__ part, const float* __restrict_
     *sp = S;
 }
 
-#define LA_PIECE 64
+#define LA_PIECE 32
 // q, k [H*D], v [H*V]: columns of proj from q_off, k_off, v_off on (element type); alpha [T][H*D] fp32 decays per token
 // and key channel, or null with head_decay [H] fp32 (one decay a head); state [slots][H][D][V] fp32; o [T][H*V] fp32.
-// pieces: null, or R * ceil(max_new / 64) * H * D * (V + 1) floats: sequences run in pieces of 64 tokens side by side
+// pieces: null, or R * ceil(max_new / 64) * H * D * (V + 1) floats: sequences run in pieces of 32 tokens side by side
 // (two passes and a chain between them).
 extern "C" int zlm_linear_attention(float* o, const void* proj, int proj_stride, int q_off, int k_off, int v_off,
                                     const float* alpha, const float* head_decay, float* state, int dtype, const int* seq_slot,

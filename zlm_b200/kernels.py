@@ -19,6 +19,7 @@ PAGE_TOKENS = 64
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 STORE, ACCUM, STORE_F32, SWIGLU = 0, 1, 2, 3
+GATED_LIMIT = 8          # g sigmoid(alpha g) (u + 1) on clamped halves; its two constants are set before the product
 GATED_GELU = 7      # as SWIGLU with gelu_tanh(gate) instead of silu(gate)
 
 
@@ -170,7 +171,7 @@ class CudaKernels:
         self._lazy_ok = False          # the next norm's output is read by products only (the arrangement's word)
         self._lazy = None              # (out, stream, weight, eps, rows times weight, sums of squares, blocks): a norm not run
         self._blank = None             # a tensor that is to be taken as zeros (see expect_blank)
-        self.gated_activations = ("silu", "gelu_tanh")      # what linear_swiglu's ``act`` takes
+        self.gated_activations = ("silu", "gelu_tanh", "swish_limit")      # what linear_swiglu's ``act`` takes
         self._scratch = {}
         self.scratch_generation = 0
         self._launches = 0
@@ -534,14 +535,26 @@ class CudaKernels:
             raise KernelError(self.lib.zlm_last_error().decode())
 
     def linear_swiglu(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None,
-                      act: str = "silu") -> None:
+                      act: str = "silu", limit: float = 0.0, alpha: float = 1.702) -> None:
         """out[t, c] = act(x[t] . gate_c) * (x[t] . up_c) in one pass over w (bf16).  w is
         [2I, K] with the rows in groups of 16: 8 gate channels, then the 8 matching up
-        channels (``interleave_gate_up``); out is [T, I].  ``act``: "silu" or "gelu_tanh"."""
+        channels (``interleave_gate_up``); out is [T, I].  ``act``: "silu", "gelu_tanh", or "swish_limit":
+        g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, -limit, limit), whose two constants a
+        one-thread kernel hands to the product's translation unit right before it."""
         T, K = x.shape
         N = w.shape[0]
         assert x.dtype == w.dtype == out.dtype == torch.bfloat16 and w.shape[1] == K and N % 16 == 0
         assert out.shape == (T, N // 2) and x.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
+        if act == "swish_limit":
+            assert limit > 0
+            if impl is None:
+                tc_ok = self.lib.zlm_gemm_tc_supported(T, N, K, x.stride(0))
+                impl = "gemv" if (self.streams_weights(T, N) or (T <= 16 and not tc_ok)) else ("tc" if tc_ok else "mma")
+            unit = {"gemv": "gemv_bf16", "tc": "gemm_tcgen05", "mma": "gemm_bf16_mma"}[impl]
+            self.flush_shares()
+            self._call("zlm_set_gate_" + unit, c_float(limit), c_float(alpha), self._stream())
+            self._bf16_product(out, x, w, T, N, K, x.stride(0), out.stride(0), GATED_LIMIT, impl)
+            return
         self._bf16_product(out, x, w, T, N, K, x.stride(0), out.stride(0),
                            {"silu": SWIGLU, "gelu_tanh": GATED_GELU}[act], impl)
 
@@ -855,9 +868,9 @@ class CudaKernels:
                    c_float(out_scale), self._stream())
 
     # -- recurrent mixers (see csrc/recurrent.cu) ---------------------------------------------------------------
-    # tokens of a sequence from which a step's recurrences run in pieces of 64 tokens side by side
+    # tokens of a sequence from which a step's recurrences run in pieces side by side, and the pieces' length
     RECURRENT_PIECES_FROM = 128
-    RECURRENT_PIECE = 64
+    RECURRENT_PIECE = 32
 
     def rglru(self, out: torch.Tensor, proj: torch.Tensor, x_off: int, y_off: int, bx: Optional[torch.Tensor],
               by: Optional[torch.Tensor], conv_w: torch.Tensor, conv_b: Optional[torch.Tensor], a_r: torch.Tensor,
@@ -908,8 +921,20 @@ class CudaKernels:
             return
         assert gates.shape == (blocks, 2 * bs, bs) and gates.is_contiguous() and gates.dtype == dt
         call(1)
-        for b in range(blocks):
-            self.linear(z[:, b], u16[:, b * bs:(b + 1) * bs], gates[b])
+        N, K, ldx, ldy = 2 * bs, bs, W, 2 * W
+        if self.bounds_check or not self.lib.zlm_gemm_tc_supported(T, N, K, ldx):
+            for b in range(blocks):
+                self.linear(z[:, b], u16[:, b * bs:(b + 1) * bs], gates[b])
+        else:
+            # the same product a block, without the host's work of ``linear`` for each (operands of one tensor each,
+            # a block's share found by address)
+            self.flush_shares()
+            ks = int(self.lib.zlm_gemm_tc_ksplit(T, N, K))
+            scratch = self.scratch("gemm_tc.partials", ks * T * N, torch.float32, z.device) if ks > 1 else None
+            pz, pu, pg, ps, st = self._p(z).value, self._p(u16).value, self._p(gates).value, self._p(scratch), self._stream()
+            for b in range(blocks):
+                self._call("zlm_gemm_tc", c_void_p(pz + b * N * 4), c_void_p(pu + b * K * 2), c_void_p(pg + b * N * K * 2),
+                           c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(STORE_F32), ps, st)
         call(2)
 
     def lowrank_decay(self, alpha: torch.Tensor, proj: torch.Tensor, lo_off: int, w2: torch.Tensor, b: Optional[torch.Tensor],
@@ -928,7 +953,7 @@ class CudaKernels:
         """o [T, heads*v_dim] fp32 = S_t^T q_t with S_t = diag(alpha_t) S_(t-1) + k_t v_t^T per head; q (times ``q_scale``),
         k, v are columns of ``proj`` from q_off, k_off, v_off on; ``alpha`` [T, heads*dim] fp32 gives a decay per token and
         key channel, or ``head_decay`` [heads] fp32 one per head; ``state`` [slots, heads, dim, v_dim] fp32.  Long prompts
-        run in pieces of 64 tokens side by side: every piece from a zero state, the pieces' states chained, and a second
+        run in pieces of 32 tokens side by side: every piece from a zero state, the pieces' states chained, and a second
         pass that adds what the state before a piece gives its tokens (``pieces`` forces or forbids that)."""
         T = proj.shape[0]
         assert o.shape == (T, heads * v_dim) and o.dtype == torch.float32 and o.is_contiguous() and proj.stride(1) == 1

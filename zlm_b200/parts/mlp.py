@@ -67,6 +67,8 @@ class SwiGLU(FeedForward):
         if self.fused:
             if self.act == "silu":
                 k.linear_swiglu(act, x, self.w_gu)
+            elif self.act == "swish_limit":
+                k.linear_swiglu(act, x, self.w_gu, act=self.act, limit=self.limit, alpha=self.alpha)
             else:
                 k.linear_swiglu(act, x, self.w_gu, act=self.act)
         else:
