@@ -123,7 +123,21 @@ rglru_gates_kernel(float* __restrict__ z, const float* __restrict__ u, const TA*
 // The same for steps of up to 16 tokens: a warp per output channel reads its two rows of the gates' matrices once
 // (lanes over the inputs), every token's sums in registers; the lanes' parts meet in a butterfly.
 #define RG_FEW 16
-template <typename TA>
+// eight neighbouring elements as floats (16 bytes of bf16, 32 of fp32; the caller has checked the alignment)
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float* f) {
+    const uint4 u = *(const uint4*)p;
+    f[0] = __uint_as_float(u.x << 16); f[1] = __uint_as_float(u.x & 0xffff0000u);
+    f[2] = __uint_as_float(u.y << 16); f[3] = __uint_as_float(u.y & 0xffff0000u);
+    f[4] = __uint_as_float(u.z << 16); f[5] = __uint_as_float(u.z & 0xffff0000u);
+    f[6] = __uint_as_float(u.w << 16); f[7] = __uint_as_float(u.w & 0xffff0000u);
+}
+__device__ __forceinline__ void load8(const float* p, float* f) {
+    const float4 a = *(const float4*)p, b = *(const float4*)(p + 4);
+    f[0] = a.x; f[1] = a.y; f[2] = a.z; f[3] = a.w; f[4] = b.x; f[5] = b.y; f[6] = b.z; f[7] = b.w;
+}
+
+// VEC 8: a lane reads eight neighbouring inputs at a time (block sizes that are multiples of 8); VEC 1: one
+template <typename TA, int VEC>
 __global__ void __launch_bounds__(256)
 rglru_gates_few_kernel(float* __restrict__ z, const float* __restrict__ u, const TA* __restrict__ Ar,
                        const TA* __restrict__ Ai, int T, int W, int bs) {
@@ -131,23 +145,28 @@ rglru_gates_few_kernel(float* __restrict__ z, const float* __restrict__ u, const
     const int lane = threadIdx.x & 31, c = blockIdx.x * 8 + (threadIdx.x >> 5);
     if (c >= W) return;
     const int b = c / bs, o = c - b * bs;
-    // (the weights are constant during a step: their loads need not wait for the kernel before)
     float acc[2][RG_FEW];
 #pragma unroll
     for (int t = 0; t < RG_FEW; ++t) acc[0][t] = acc[1][t] = 0.f;
     pdl_wait();
-    for (int i = lane; i < bs; i += 32) {
+    for (int i = lane * VEC; i < bs; i += 32 * VEC) {
         const TA* pr = Ar + (size_t)c * bs + i;
         const TA* pi = Ai + (size_t)c * bs + i;
-        if (!ZLM_CHK(pr, sizeof(TA)) || !ZLM_CHK(pi, sizeof(TA))) continue;
-        const float wr = to_f32(*pr), wi = to_f32(*pi);
+        if (!ZLM_CHK(pr, VEC * sizeof(TA)) || !ZLM_CHK(pi, VEC * sizeof(TA))) continue;
+        float wr[VEC], wi[VEC];
+        if (VEC == 8) { load8(pr, wr); load8(pi, wi); } else { wr[0] = to_f32(*pr); wi[0] = to_f32(*pi); }
 #pragma unroll
         for (int t = 0; t < RG_FEW; ++t) {
             if (t >= T) break;
             const float* up = u + (size_t)t * W + b * bs + i;
-            const float x = ZLM_CHK(up, 4) ? *up : 0.f;
-            acc[0][t] = fmaf(wr, x, acc[0][t]);
-            acc[1][t] = fmaf(wi, x, acc[1][t]);
+            if (!ZLM_CHK(up, VEC * 4)) continue;
+            float x[VEC];
+            if (VEC == 8) load8(up, x); else x[0] = *up;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                acc[0][t] = fmaf(wr[e], x[e], acc[0][t]);
+                acc[1][t] = fmaf(wi[e], x[e], acc[1][t]);
+            }
         }
     }
 #pragma unroll
@@ -368,8 +387,13 @@ static void launch_rglru(void* out, int out_stride, float* u, void* u16, float* 
                    seq_start, cu_seqlens, W, taps);
     if (phase == 1) return;
     if (!gates_done) {
-        if (T <= RG_FEW)
-            zlm_launch(rglru_gates_few_kernel<TA>, dim3((W + 7) / 8), dim3(256), 0, st, z, (const float*)u, (const TA*)Ar,
+        // (eight inputs a lane where every row of a block starts at a multiple of 16 bytes, and u's rows at 32)
+        const bool vec = bs % 8 == 0 && (uintptr_t)Ar % 16 == 0 && (uintptr_t)Ai % 16 == 0 && (uintptr_t)u % 16 == 0;
+        if (T <= RG_FEW && vec)
+            zlm_launch(rglru_gates_few_kernel<TA, 8>, dim3((W + 7) / 8), dim3(256), 0, st, z, (const float*)u, (const TA*)Ar,
+                       (const TA*)Ai, T, W, bs);
+        else if (T <= RG_FEW)
+            zlm_launch(rglru_gates_few_kernel<TA, 1>, dim3((W + 7) / 8), dim3(256), 0, st, z, (const float*)u, (const TA*)Ar,
                        (const TA*)Ai, T, W, bs);
         else
             zlm_launch(rglru_gates_kernel<TA>, dim3((T + RG_TT - 1) / RG_TT, (bs + RG_OT - 1) / RG_OT, blocks), dim3(RG_OT * 4), 0,
@@ -431,40 +455,57 @@ extern "C" int zlm_rglru(void* out, int out_stride, float* u, void* u16, float* 
 // ---------------------------------------------------------------------------- decays from a low-rank projection
 // alpha[t][c] = sigmoid(z)^(1/tau) = exp(-softplus(-z) / tau), z = sum_r W2[c][r] lo[t][r] + b[c]; lo: `rank` columns of
 // proj from lo_off on.  fp32 throughout.
-template <typename TA>
+// TOK tokens a block: a thread reads its channel's row of W2 once for all of them
+template <typename TA, int TOK>
 __global__ void __launch_bounds__(256)
 lowrank_decay_kernel(float* __restrict__ alpha, const TA* __restrict__ proj, int proj_stride, int lo_off, const TA* __restrict__ W2,
-                     const TA* __restrict__ b, int C, int rank, float inv_tau) {
-    extern __shared__ float ld_lo[];
+                     const TA* __restrict__ b, int T, int C, int rank, float inv_tau) {
+    extern __shared__ float ld_lo[];            // [TOK][rank]
     pdl_trigger();
-    const int t = blockIdx.x;
+    const int t0 = blockIdx.x * TOK;
     pdl_wait();
-    for (int r = threadIdx.x; r < rank; r += blockDim.x) {
-        const TA* p = proj + (size_t)t * proj_stride + lo_off + r;
-        ld_lo[r] = ZLM_CHK(p, sizeof(TA)) ? to_f32(*p) : 0.f;
+    for (int x = threadIdx.x; x < TOK * rank; x += blockDim.x) {
+        const int tt = x / rank, r = x - tt * rank;
+        const TA* p = proj + (size_t)(t0 + tt) * proj_stride + lo_off + r;
+        ld_lo[x] = (t0 + tt < T && ZLM_CHK(p, sizeof(TA))) ? to_f32(*p) : 0.f;
     }
     __syncthreads();
     for (int c = threadIdx.x; c < C; c += blockDim.x) {
-        float z = b ? to_f32(b[c]) : 0.f;
-        for (int r = 0; r < rank; ++r)
-            if (ZLM_CHK(W2 + (size_t)c * rank + r, sizeof(TA))) z = fmaf(to_f32(W2[(size_t)c * rank + r]), ld_lo[r], z);
-        if (ZLM_CHK(alpha + (size_t)t * C + c, 4)) alpha[(size_t)t * C + c] = expf(-softplus_f(-z) * inv_tau);
+        float z[TOK];
+        const float bias = b ? to_f32(b[c]) : 0.f;
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) z[tt] = bias;
+        for (int r = 0; r < rank; ++r) {
+            if (!ZLM_CHK(W2 + (size_t)c * rank + r, sizeof(TA))) continue;
+            const float w = to_f32(W2[(size_t)c * rank + r]);
+#pragma unroll
+            for (int tt = 0; tt < TOK; ++tt) z[tt] = fmaf(w, ld_lo[tt * rank + r], z[tt]);
+        }
+#pragma unroll
+        for (int tt = 0; tt < TOK; ++tt) {
+            if (t0 + tt >= T) break;
+            float* ap = alpha + (size_t)(t0 + tt) * C + c;
+            if (ZLM_CHK(ap, 4)) *ap = expf(-softplus_f(-z[tt]) * inv_tau);
+        }
     }
 }
 
 extern "C" int zlm_lowrank_decay(float* alpha, const void* proj, int proj_stride, int lo_off, const void* W2, const void* b,
                                  int dtype, int T, int C, int rank, float tau, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
-    ZLM_REQUIRE(C > 0 && rank > 0 && rank <= 8192 && tau > 0.f, "lowrank_decay: %d channels of rank %d, tau %g", C, rank, (double)tau);
-    const size_t smem = (size_t)rank * sizeof(float);
-    if (dtype == ZLM_DTYPE_F32)
-        zlm_launch(lowrank_decay_kernel<float>, dim3(T), dim3(256), smem, st, alpha, (const float*)proj, proj_stride, lo_off,
-                   (const float*)W2, (const float*)b, C, rank, 1.0f / tau);
-    else if (dtype == ZLM_DTYPE_BF16)
-        zlm_launch(lowrank_decay_kernel<__nv_bfloat16>, dim3(T), dim3(256), smem, st, alpha, (const __nv_bfloat16*)proj,
-                   proj_stride, lo_off, (const __nv_bfloat16*)W2, (const __nv_bfloat16*)b, C, rank, 1.0f / tau);
-    else
+    ZLM_REQUIRE(C > 0 && rank > 0 && rank <= 512 && tau > 0.f, "lowrank_decay: %d channels of rank %d, tau %g", C, rank, (double)tau);
+    // many tokens: sixteen a block; few: one, so that the blocks are many
+#define ZLM_LD(TA, TOK)                                                                                                  \
+    zlm_launch(lowrank_decay_kernel<TA, TOK>, dim3((T + TOK - 1) / TOK), dim3(256), (size_t)TOK * rank * sizeof(float), st, alpha, \
+               (const TA*)proj, proj_stride, lo_off, (const TA*)W2, (const TA*)b, T, C, rank, 1.0f / tau)
+    if (dtype == ZLM_DTYPE_F32) {
+        if (T >= 256) ZLM_LD(float, 16); else ZLM_LD(float, 1);
+    } else if (dtype == ZLM_DTYPE_BF16) {
+        if (T >= 256) ZLM_LD(__nv_bfloat16, 16); else ZLM_LD(__nv_bfloat16, 1);
+    } else {
         ZLM_REQUIRE(false, "lowrank_decay: unsupported dtype %d", dtype);
+    }
+#undef ZLM_LD
     return zlm_check_launch("lowrank_decay");
 }
 

@@ -306,6 +306,7 @@ attn_prep_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __restrict_
     float* val = ap_smem;
     float* inv = ap_smem + C;
     float* red = inv + nq + nkv;
+    float* rot = red + 32;                      // [n_rot/2] cosines, [n_rot/2] sines of the token's angles
     pdl_wait();
     if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4) || !ZLM_CHK(token_seq + t, 4)) return;
     const int pos = token_pos[t], slot = token_slot[t], r = token_seq[t];
@@ -348,9 +349,16 @@ attn_prep_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __restrict_
             if (lane == 0) inv[h] = norm_mode ? 1.0f / sqrtf(ss / (float)dim + eps) : 1.0f;
         }
     }
+    // the token's angles once a block: fp32 angle, sine and cosine, times the table's factor
+    const int half = n_rot / 2;
+    for (int f = tid; f < half; f += AP_THREADS) {
+        float sn, cs;
+        sincosf((float)pos * inv_freq[f], &sn, &cs);
+        rot[f] = cs * rot_scale;
+        rot[half + f] = sn * rot_scale;
+    }
     __syncthreads();
     // q and k heads: norm, weight, rotation, write
-    const int half = n_rot / 2;
     int page = 0;
     if (ZLM_CHK(block_table + (size_t)slot * table_stride + pos / ZLM_PAGE, 4))
         page = block_table[(size_t)slot * table_stride + pos / ZLM_PAGE];
@@ -369,9 +377,7 @@ attn_prep_kernel(TA* __restrict__ q_out, int q_out_stride, const TA* __restrict_
                     const int fi = e < half ? e : e - half;
                     const int pe = e < half ? e + half : e - half;
                     const float other = val[unit * dim + pe] * sc * (norm_mode >= 2 ? w[wb + pe] : 1.0f);
-                    float sn, cs;
-                    sincosf((float)pos * inv_freq[fi], &sn, &cs);
-                    sn *= rot_scale; cs *= rot_scale;
+                    const float cs = rot[fi], sn = rot[half + fi];
                     o = e < half ? o * cs - other * sn : o * cs + other * sn;
                 }
             }
@@ -397,7 +403,7 @@ static void launch_attn_prep(void* q_out, int q_out_stride, const void* proj, in
                              int T, int R, int nq, int nkv, int dim, int vdim, int hdp, int taps, int norm_mode, VecW q_w,
                              VecW k_w, float eps, const float* inv_freq, int n_rot, float rot_scale, cudaStream_t st) {
     const int C = (nq + nkv) * dim + nkv * vdim;
-    const size_t smem = (size_t)(C + nq + nkv + 32) * sizeof(float);
+    const size_t smem = (size_t)(C + nq + nkv + 32 + n_rot) * sizeof(float);
     // blocks a token: one where the tokens alone fill the device, else as many as give it two rounds of work
     int share = 1;
     const int outputs = (nq + 2 * nkv) * hdp;
@@ -427,7 +433,7 @@ extern "C" int zlm_attn_prep(void* q_out, int q_out_stride, const void* proj, in
     ZLM_REQUIRE(!conv_w || taps == 1 || state, "attn_prep: a convolution of %d taps needs the sequences' state", taps);
     ZLM_REQUIRE(norm_mode >= 0 && norm_mode <= 3 && (norm_mode < 2 || (q_w && k_w)), "attn_prep: norm mode %d", norm_mode);
     ZLM_REQUIRE(n_rot >= 0 && n_rot % 2 == 0 && n_rot <= dim && (n_rot == 0 || inv_freq), "attn_prep: rotation over %d of %d coordinates", n_rot, dim);
-    const size_t smem = (size_t)((nq + nkv) * dim + nkv * vdim + nq + nkv + 32) * sizeof(float);
+    const size_t smem = (size_t)((nq + nkv) * dim + nkv * vdim + nq + nkv + 32 + n_rot) * sizeof(float);
     ZLM_REQUIRE(smem <= 200 * 1024, "attn_prep: %zu bytes of channels a token", smem);
     const VecW qw{q_w, w_dtype}, kw{k_w, w_dtype};
     if (dtype == ZLM_DTYPE_F32) {
