@@ -190,3 +190,15 @@ def test_command_line_writes_and_runs_a_random_model(tmp_path, capsys):
         got[int(req)].append(int(tok))
     want = Engine.from_pretrained(folder, dtype="float32", max_tokens=256).generate([[5, 17, 3], [9, 9]], max_tokens=6).tokens
     assert [got[0], got[1]] == want
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_a_batch_of_many_requests_through_captured_steps(tmp_path, name):
+    """24 unequal requests generated together (decode steps of more than 16 rows: the many-token forms of the kernels
+    inside captured steps) give, in 32-bit, the tokens that each request gives alone."""
+    eng, cfg, _ = build(tmp_path, name, "float32", max_tokens=64 * 64, max_batch=32)
+    ps = prompts(cfg["vocab"], [3 + (7 * i) % 40 for i in range(24)], seed=9)
+    together = eng.generate(ps, max_tokens=10).tokens
+    alone = [eng.generate([p], max_tokens=10).tokens[0] for p in ps]
+    assert together == alone
+    eng.check(sync=True)
