@@ -177,6 +177,98 @@ extern "C" int zlm_norm_scale_add(float* stream, const void* y, int y_dtype, con
     return zlm_check_launch("norm_scale_add");
 }
 
+// ---------------------------------------------------------------- the same, and the norm that reads the stream next
+// stream += y / rms(y) * w1, then out2 = stream / rms(stream) * w2 in the element type: a layer that norms a sublayer's
+// output and the next sublayer's input does both in one pass over the row, which is held in shared memory as fp32.
+// One block per row, its size a function of H alone.
+template <typename TO>
+__global__ void norm_add_norm_kernel(float* __restrict__ stream, const float* __restrict__ y, VecW w1, float eps1,
+                                     TO* __restrict__ out2, VecW w2, float eps2, int H, int in_regs) {
+    extern __shared__ float nan_row[];          // [32] reduction, then (rows that do not fit the registers) [H] the row
+    float* red = nan_row;
+    float* row = nan_row + 32;
+    pdl_trigger();
+    const int r = blockIdx.x;
+    pdl_wait();
+    float* xr = stream + (size_t)r * H;
+    const float* yr = y + (size_t)r * H;
+    TO* orow = out2 + (size_t)r * H;
+    if (!ZLM_CHK(xr, (size_t)H * 4) || !ZLM_CHK(yr, (size_t)H * 4) || !ZLM_CHK(orow, (size_t)H * sizeof(TO))) return;
+    if (in_regs) {
+        // H a multiple of 4 and up to NORM_MAX_V4 float4 a thread: the row is read once and stays in registers
+        const int nv = H / 4;
+        float4 v[NORM_MAX_V4], x[NORM_MAX_V4];
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < NORM_MAX_V4; ++j) {
+            const int c = threadIdx.x + j * blockDim.x;
+            v[j] = c < nv ? *(const float4*)(yr + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            x[j] = c < nv ? *(const float4*)(xr + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            s = fmaf(v[j].x, v[j].x, s); s = fmaf(v[j].y, v[j].y, s);
+            s = fmaf(v[j].z, v[j].z, s); s = fmaf(v[j].w, v[j].w, s);
+        }
+        const float inv1 = 1.0f / sqrtf(block_sum(s, red) / (float)H + eps1);
+        float s2 = 0.f;
+#pragma unroll
+        for (int j = 0; j < NORM_MAX_V4; ++j) {
+            const int c = threadIdx.x + j * blockDim.x;
+            if (c >= nv) continue;
+            const float4 wv = w1.load4(c * 4);
+            float4 a = x[j];
+            a.x += (v[j].x * inv1) * wv.x; a.y += (v[j].y * inv1) * wv.y;
+            a.z += (v[j].z * inv1) * wv.z; a.w += (v[j].w * inv1) * wv.w;
+            *(float4*)(xr + c * 4) = a;
+            v[j] = a;
+            s2 = fmaf(a.x, a.x, s2); s2 = fmaf(a.y, a.y, s2); s2 = fmaf(a.z, a.z, s2); s2 = fmaf(a.w, a.w, s2);
+        }
+        const float inv2 = 1.0f / sqrtf(block_sum(s2, red) / (float)H + eps2);
+#pragma unroll
+        for (int j = 0; j < NORM_MAX_V4; ++j) {
+            const int c = threadIdx.x + j * blockDim.x;
+            if (c >= nv) continue;
+            const float4 wv = w2.load4(c * 4);
+            store4(orow + c * 4, (v[j].x * inv2) * wv.x, (v[j].y * inv2) * wv.y, (v[j].z * inv2) * wv.z, (v[j].w * inv2) * wv.w);
+        }
+        return;
+    }
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float a = yr[i];
+        row[i] = a;
+        s = fmaf(a, a, s);
+    }
+    const float inv1 = 1.0f / sqrtf(block_sum(s, red) / (float)H + eps1);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float a = xr[i] + (row[i] * inv1) * w1[i];
+        xr[i] = a;
+        row[i] = a;
+        s2 = fmaf(a, a, s2);
+    }
+    const float inv2 = 1.0f / sqrtf(block_sum(s2, red) / (float)H + eps2);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) orow[i] = from_f32<TO>((row[i] * inv2) * w2[i]);
+}
+
+extern "C" int zlm_norm_add_norm(float* stream, const float* y, const void* w1, int w1_dtype, float eps1, void* out2,
+                                 int out2_dtype, const void* w2, int w2_dtype, float eps2, int R, int H, cudaStream_t st) {
+    if (R == 0) return ZLM_OK;
+    ZLM_REQUIRE(R > 0 && H > 0 && H <= 11264, "norm_add_norm: bad sizes R=%d H=%d (rows of up to 11264)", R, H);
+    int threads = 128;
+    while (threads < 1024 && threads * 4 * NORM_MAX_V4 < H) threads *= 2;
+    const int in_regs = (H % 4 == 0 && H / 4 <= NORM_MAX_V4 * threads && (uintptr_t)stream % 16 == 0 && (uintptr_t)y % 16 == 0 &&
+                         (uintptr_t)w1 % 16 == 0 && (uintptr_t)w2 % 16 == 0 && (uintptr_t)out2 % 16 == 0) ? 1 : 0;
+    const size_t smem = (size_t)(32 + (in_regs ? 0 : H)) * sizeof(float);
+    const VecW v1{w1, w1_dtype}, v2{w2, w2_dtype};
+    if (out2_dtype == ZLM_DTYPE_F32)
+        zlm_launch(norm_add_norm_kernel<float>, R, threads, smem, st, stream, y, v1, eps1, (float*)out2, v2, eps2, H, in_regs);
+    else if (out2_dtype == ZLM_DTYPE_BF16)
+        zlm_launch(norm_add_norm_kernel<__nv_bfloat16>, R, threads, smem, st, stream, y, v1, eps1, (__nv_bfloat16*)out2, v2,
+                   eps2, H, in_regs);
+    else
+        ZLM_REQUIRE(false, "norm_add_norm: unsupported output dtype %d", out2_dtype);
+    return zlm_check_launch("norm_add_norm");
+}
+
 // ---------------------------------------------------------------- the stream's rows in the compute dtype
 __global__ void cast_rows_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ x, size_t n4, size_t n) {
     pdl_launch_dependents();

@@ -1170,6 +1170,21 @@ class CudaKernels:
                    self._p(layer_scale), c_int(_dt(layer_scale) if layer_scale is not None else F32), c_int(R), c_int(H),
                    c_float(eps), self._p(cast_out), self._stream())
 
+    NORM_ADD_NORM_MAX = 11264        # the widest row the fused pair of norms holds in shared memory
+
+    def norm_add_norm(self, stream: torch.Tensor, y: torch.Tensor, w1: torch.Tensor, eps1: float, out2: torch.Tensor,
+                      w2: torch.Tensor, eps2: float) -> None:
+        """stream[t] += y[t] / sqrt(mean(y[t]^2) + eps1) * w1, then out2[t] = stream[t] / sqrt(mean(stream[t]^2) + eps2)
+        * w2 (the compute dtype): a sublayer's closing norm with its residual add, and the next sublayer's opening norm,
+        in one kernel.  y fp32."""
+        R, H = stream.shape
+        assert stream.dtype == y.dtype == torch.float32 and y.shape == (R, H) and out2.shape == (R, H)
+        assert stream.is_contiguous() and y.is_contiguous() and out2.is_contiguous() and H <= self.NORM_ADD_NORM_MAX
+        assert w1.shape == (H,) and w2.shape == (H,) and w1.is_contiguous() and w2.is_contiguous()
+        self._call("zlm_norm_add_norm", self._p(stream), self._p(y), self._p(w1), c_int(_dt(w1)), c_float(eps1),
+                   self._p(out2), c_int(_dt(out2)), self._p(w2), c_int(_dt(w2)), c_float(eps2), c_int(R), c_int(H),
+                   self._stream())
+
     def cast_rows(self, out: torch.Tensor, x: torch.Tensor) -> None:
         """out = x rounded to bfloat16 (x fp32, both contiguous and of one shape)."""
         assert x.dtype == torch.float32 and out.dtype == torch.bfloat16 and out.shape == x.shape

@@ -142,7 +142,9 @@ class SublayerNormBlock(Part):
 class SandwichNormBlock(Part):
     """x <- x + post1(mixer(pre1(x))), then x <- x + post2(ffn(pre2(x))).  The sublayer reads the normed rows (compute
     dtype) and "adds its result" into a scratch row per token that counts as zeros (``expect_blank``); the second norm
-    norms that row and adds it into the fp32 stream in one kernel (``Norm.add_into``)."""
+    norms that row and adds it into the fp32 stream in one kernel (``Norm.add_into``), and where the next reader of the
+    stream is a norm of the same kind (the feed-forward's, or the next block's first) that kernel leaves its rows too
+    (``add_into_then_norm``), so that a layer launches two norm kernels, not four."""
 
     def __init__(self, hidden_size: int, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm,
                  mixer_post_norm: Norm, feed_forward_post_norm: Optional[Norm] = None):
@@ -165,13 +167,20 @@ class SandwichNormBlock(Part):
     step_key = PreNormBlock.step_key
 
     def first_norm_weight(self):
-        return None             # (the block before is told nothing: this block's norms are always run)
+        return None             # (no product is told of this block's first norm: see ``first_norm``)
 
-    def _sublayer(self, pre: Norm, post: Norm, hidden: torch.Tensor, run) -> None:
+    def first_norm(self) -> Norm:
+        """The norm that reads the stream first in this block: a block of this arrangement before it may run it together
+        with its own closing norm."""
+        return self.mixer_norm
+
+    def _sublayer(self, pre: Norm, post: Norm, nxt, hidden: torch.Tensor, run, ctx: StepContext) -> None:
         rt, k = self.rt, self.rt.k
         self.finish_products()
         x = rt.ws.get("block.normed", hidden.shape, rt.dtype)
-        pre.forward(x, hidden)
+        # (the norm that closed the sublayer before may have left this norm's rows there)
+        if ctx.extras.pop("stream.normed", None) != (x.data_ptr(), id(pre)):
+            pre.forward(x, hidden)
         y = rt.ws.get("block.sublayer_out", hidden.shape, torch.float32)
         blank = getattr(k, "expect_blank", None)
         if blank is not None:
@@ -181,7 +190,13 @@ class SandwichNormBlock(Part):
         run(x, y)
         if blank is not None:
             blank(None)
-        post.add_into(hidden, y)
+        # the closing norm, the residual add and, where the next reader of the stream is a norm of the same kind, that
+        # norm too (the sublayer is done with x: its rows may be written anew)
+        fuse = getattr(post, "add_into_then_norm", None)
+        if nxt is not None and fuse is not None and fuse(hidden, y, nxt, x):
+            ctx.extras["stream.normed"] = (x.data_ptr(), id(nxt))
+        else:
+            post.add_into(hidden, y)
 
     def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
         ctx.extras.pop("stream.rounded", None)
@@ -189,6 +204,9 @@ class SandwichNormBlock(Part):
             say = getattr(self.rt.k, word, None)
             if say is not None:
                 say(None if word == "expect_norm" else False)
-        self._sublayer(self.mixer_norm, self.mixer_post, hidden, lambda x, y: self.mixer.forward(x, y, ctx, io))
-        if not getattr(self.ffn, "is_identity", False):
-            self._sublayer(self.ffn_norm, self.ffn_post, hidden, lambda x, y: self.ffn.forward(x, y, ctx))
+        after = ctx.extras.get("first_norm_after_block")           # the model's word: the next block's first norm, if it has one to offer
+        has_ffn = not getattr(self.ffn, "is_identity", False)
+        self._sublayer(self.mixer_norm, self.mixer_post, self.ffn_norm if has_ffn else after, hidden,
+                       lambda x, y: self.mixer.forward(x, y, ctx, io), ctx)
+        if has_ffn:
+            self._sublayer(self.ffn_norm, self.ffn_post, after, hidden, lambda x, y: self.ffn.forward(x, y, ctx), ctx)

@@ -141,6 +141,7 @@ class DecoderModel:
         # (the embedding writes the stream anew: whatever a run before this one, with the same context, noted about
         # copies of the stream, as the eager run before a capture does, no longer holds)
         ctx.extras.pop("stream.rounded", None)
+        ctx.extras.pop("stream.normed", None)
         if getattr(self.embedding, "uses_step", False):
             self.embedding.forward(hidden, ctx.token_ids, ctx, embedding_io)
         else:
@@ -152,9 +153,13 @@ class DecoderModel:
             nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
             first = getattr(nxt, "first_norm_weight", None)
             ctx.extras["norm_after_block"] = first() if first is not None else None
+            first_part = getattr(nxt, "first_norm", None)
+            ctx.extras["first_norm_after_block"] = first_part() if first_part is not None else None
             self.blocks[e.layer].forward(hidden, ctx, io)
         ctx.extras["norm_after_block"] = None
+        ctx.extras["first_norm_after_block"] = None
         ctx.extras.pop("stream.rounded", None)
+        ctx.extras.pop("stream.normed", None)
         return hidden
 
     def logits(self, hidden: torch.Tensor, rows: torch.Tensor, n_rows: int,

@@ -78,6 +78,17 @@ class RMSNorm(Norm):
         return True
 
 
+    def add_into_then_norm(self, stream: torch.Tensor, y: torch.Tensor, nxt: Norm, out: torch.Tensor) -> bool:
+        """stream += norm(y) and out = nxt(stream) in one kernel, if both norms are of this kind without a scale of
+        their own and the kernel object has the kernel; the answer says whether it was done (else nothing was)."""
+        fused = getattr(self.rt.k, "norm_add_norm", None)
+        if (fused is None or not isinstance(nxt, RMSNorm) or self.layer_scale or nxt.layer_scale or y.dtype != torch.float32
+                or self.size > getattr(self.rt.k, "NORM_ADD_NORM_MAX", 0)):
+            return False
+        fused(stream, y, self.weight, self.eps, out, nxt.weight, nxt.eps)
+        return True
+
+
 @register_norm("none")
 class NoNorm(Norm):
     """Stands where a layer has nothing to norm (a layer without a feed-forward): no tensors, never run."""

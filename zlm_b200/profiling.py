@@ -286,6 +286,10 @@ class ProfilingKernels:
         return self._timed(kind, n, 6.0 * T * heads * dim * v_dim, self.k.linear_attention, o, proj, q_off, k_off, v_off,
                            alpha, head_decay, state, plan, heads, dim, v_dim, *args, **kw)
 
+    def norm_add_norm(self, stream, y, w1, eps1, out2, w2, eps2):
+        return self._timed("sublayer norm+add+next norm", 3 * _nbytes(stream) + _nbytes(out2), 0, self.k.norm_add_norm,
+                           stream, y, w1, eps1, out2, w2, eps2)
+
     def scaled_sum(self, out, a, alpha, b, beta, accumulate=True):
         return self._timed("two sides summed", 3 * _nbytes(out), 0, self.k.scaled_sum, out, a, alpha, b, beta, accumulate)
 
